@@ -93,6 +93,12 @@ def _register_builtin() -> None:
         name="Gonozen", model_type="gonozen", config_cls=GonozenConfig,
         decoder_spec=gonozen.decoder_spec, weight_sources=gonozen.weight_sources,
         ignorable_tensors=gonozen.ignorable_tensors, checkpoint_shapes=gonozen.checkpoint_shapes))
+    from ..models import nozizen
+    from .nozizen_config import NozizenConfig
+    register_architecture(Architecture(
+        name="Nozizen", model_type="nozizen", config_cls=NozizenConfig,
+        decoder_spec=nozizen.decoder_spec, weight_sources=nozizen.weight_sources,
+        ignorable_tensors=nozizen.ignorable_tensors, checkpoint_shapes=nozizen.checkpoint_shapes))
 
 
 _register_builtin()

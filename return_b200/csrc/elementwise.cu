@@ -7,32 +7,33 @@
 #include "common.cuh"
 
 // ---------------------------------------------------------------- embedding
-// stream[t, :] = float(table[tokens[t], :]).  A token id outside [0, V) writes NaN so that the
+// stream[t, c, :] = scale * float(table[tokens[t], :]) for each of `copies` copies c (a model that keeps several
+// residual streams starts them all from the embedded token).  A token id outside [0, V) writes NaN so that the
 // fault shows in the logits instead of reading foreign memory.
 template <typename TW>
 __global__ void embedding_kernel(const TW* __restrict__ table, const int* __restrict__ tokens,
-                                 float* __restrict__ stream, int H, int V) {
+                                 float* __restrict__ stream, int H, int V, float scale, int copies) {
     const int t = blockIdx.x;
     const int id = tokens[t];
-    float* dst = stream + (size_t)t * H;
-    if (id < 0 || id >= V) {
-        for (int i = threadIdx.x; i < H; i += blockDim.x) dst[i] = __int_as_float(0x7fc00000);
-        return;
+    float* dst = stream + (size_t)t * copies * H;
+    const bool bad = id < 0 || id >= V;
+    const TW* src = table + (size_t)(bad ? 0 : id) * H;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+        const float v = bad ? __int_as_float(0x7fc00000) : to_f32(src[i]) * scale;
+        for (int c = 0; c < copies; ++c) dst[(size_t)c * H + i] = v;
     }
-    const TW* src = table + (size_t)id * H;
-    for (int i = threadIdx.x; i < H; i += blockDim.x) dst[i] = to_f32(src[i]);
 }
 
 // Sixteen bytes of the table per thread and iteration, for rows whose length allows it.
 template <typename TW>
 __global__ void embedding_vec_kernel(const TW* __restrict__ table, const int* __restrict__ tokens,
-                                     float* __restrict__ stream, int H, int V) {
+                                     float* __restrict__ stream, int H, int V, float scale, int copies) {
     constexpr int E = 16 / sizeof(TW);
     pdl_launch_dependents();
     pdl_wait();
     const int t = blockIdx.x;
     const int id = tokens[t];
-    float* dst = stream + (size_t)t * H;
+    float* dst = stream + (size_t)t * copies * H;
     const bool bad = id < 0 || id >= V;
     const TW* src = table + (size_t)(bad ? 0 : id) * H;
     for (int i = threadIdx.x * E; i < H; i += blockDim.x * E) {
@@ -40,28 +41,31 @@ __global__ void embedding_vec_kernel(const TW* __restrict__ table, const int* __
         const TW* e = reinterpret_cast<const TW*>(&raw);
         float out[E];
 #pragma unroll
-        for (int k = 0; k < E; ++k) out[k] = bad ? __int_as_float(0x7fc00000) : to_f32(e[k]);
+        for (int k = 0; k < E; ++k) out[k] = bad ? __int_as_float(0x7fc00000) : to_f32(e[k]) * scale;
+        for (int c = 0; c < copies; ++c) {
 #pragma unroll
-        for (int k = 0; k < E; k += 4)
-            *reinterpret_cast<float4*>(dst + i + k) = make_float4(out[k], out[k + 1], out[k + 2], out[k + 3]);
+            for (int k = 0; k < E; k += 4)
+                *reinterpret_cast<float4*>(dst + (size_t)c * H + i + k) = make_float4(out[k], out[k + 1], out[k + 2], out[k + 3]);
+        }
     }
 }
 
 RB_EXPORT int rb_embedding(const void* table, int table_dtype, const int* tokens, float* stream,
-                           int T, int H, int V, cudaStream_t st) {
+                           int T, int H, int V, float scale, int copies, cudaStream_t st) {
     if (T <= 0) return 0;
+    if (copies < 1) return (int)cudaErrorInvalidValue;
     const int threads = H >= 1024 ? 256 : 128;
     const bool aligned = ((uintptr_t)table % 16) == 0 && ((uintptr_t)stream % 16) == 0;
     if (table_dtype == RB_F32) {
         if (aligned && H % 4 == 0)
-            return rb_launch_pdl(embedding_vec_kernel<float>, dim3(T), dim3(threads), 0, st, (const float*)table, tokens, stream, H, V);
+            return rb_launch_pdl(embedding_vec_kernel<float>, dim3(T), dim3(threads), 0, st, (const float*)table, tokens, stream, H, V, scale, copies);
         else
-            embedding_kernel<float><<<T, threads, 0, st>>>((const float*)table, tokens, stream, H, V);
+            embedding_kernel<float><<<T, threads, 0, st>>>((const float*)table, tokens, stream, H, V, scale, copies);
     } else {
         if (aligned && H % 8 == 0)
-            return rb_launch_pdl(embedding_vec_kernel<bf16>, dim3(T), dim3(threads), 0, st, (const bf16*)table, tokens, stream, H, V);
+            return rb_launch_pdl(embedding_vec_kernel<bf16>, dim3(T), dim3(threads), 0, st, (const bf16*)table, tokens, stream, H, V, scale, copies);
         else
-            embedding_kernel<bf16><<<T, threads, 0, st>>>((const bf16*)table, tokens, stream, H, V);
+            embedding_kernel<bf16><<<T, threads, 0, st>>>((const bf16*)table, tokens, stream, H, V, scale, copies);
     }
     return rb_launch_status();
 }
@@ -403,4 +407,193 @@ RB_EXPORT int rb_softcap(float* x, float cap, long long total, cudaStream_t st) 
     if (total <= 0) return 0;
     const int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
     return rb_launch_pdl(softcap_kernel, dim3(blocks), dim3(256), 0, st, x, cap, total);
+}
+
+// ---------------------------------------------------------------- one-argument activations over rows
+// out[r, c] = f(x[r, c]) for rows of `cols` elements with their own strides; in place when out == x.
+//   0: relu(x)^2    1: tanh(x)    2: 0.5 x (1 + tanh(sqrt(2/pi) (x + 0.044715 x^3)))    3: x sigmoid(x)
+//   4: exp(-exp(x + b[c])): a decay in (0, 1) from its doubly logarithmic form, with a bias per column
+// Arithmetic in float32; the input and the output each float32 or bfloat16.
+#define ACT_RELU2 0
+#define ACT_TANH 1
+#define ACT_GELU_TANH 2
+#define ACT_SILU 3
+#define ACT_NEG_EXP_EXP 4
+
+template <typename TI, typename TO>
+__global__ void activation_kernel(const TI* __restrict__ x, long long ldx, TO* __restrict__ out, long long ldo, int op,
+                                  const void* __restrict__ bias, int bias_dtype, int rows, int cols) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const long long total = (long long)rows * cols;
+    for (long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += (long long)gridDim.x * blockDim.x) {
+        const long long r = e / cols;
+        const int c = (int)(e - r * cols);
+        const float v = to_f32(x[r * ldx + c]);
+        float y;
+        if (op == ACT_RELU2) { const float p = fmaxf(v, 0.f); y = p * p; }
+        else if (op == ACT_TANH) y = tanhf(v);
+        else if (op == ACT_GELU_TANH) y = 0.5f * v * (1.0f + tanhf(0.7978845608028654f * (v + 0.044715f * v * v * v)));
+        else if (op == ACT_SILU) y = v / (1.0f + expf(-v));
+        else y = expf(-expf(v + (bias ? load_as_f32(bias, bias_dtype, c) : 0.f)));
+        out[r * ldo + c] = from_f32<TO>(y);
+    }
+}
+
+RB_EXPORT int rb_activation(const void* x, long long ldx, int x_dtype, void* out, long long ldo, int out_dtype, int op,
+                            const void* bias, int bias_dtype, int rows, int cols, cudaStream_t st) {
+    if (rows <= 0 || cols <= 0) return 0;
+    if (op < 0 || op > ACT_NEG_EXP_EXP) return (int)cudaErrorInvalidValue;
+    const long long total = (long long)rows * cols;
+    const int blocks = (int)((total + 255) / 256 < 8192 ? (total + 255) / 256 : 8192);
+    if (x_dtype == RB_F32 && out_dtype == RB_F32)
+        return rb_launch_pdl(activation_kernel<float, float>, dim3(blocks), dim3(256), 0, st, (const float*)x, ldx, (float*)out, ldo, op, bias, bias_dtype, rows, cols);
+    if (x_dtype == RB_F32)
+        return rb_launch_pdl(activation_kernel<float, bf16>, dim3(blocks), dim3(256), 0, st, (const float*)x, ldx, (bf16*)out, ldo, op, bias, bias_dtype, rows, cols);
+    if (out_dtype == RB_F32)
+        return rb_launch_pdl(activation_kernel<bf16, float>, dim3(blocks), dim3(256), 0, st, (const bf16*)x, ldx, (float*)out, ldo, op, bias, bias_dtype, rows, cols);
+    return rb_launch_pdl(activation_kernel<bf16, bf16>, dim3(blocks), dim3(256), 0, st, (const bf16*)x, ldx, (bf16*)out, ldo, op, bias, bias_dtype, rows, cols);
+}
+
+// ---------------------------------------------------------------- several residual streams (hyper-connections)
+// A token's residual is S streams x_0 .. x_(S-1), stored [T, S, H] in float32.  A sublayer reads one weighted sum of
+// them and writes back into all of them:
+//     read:   u = sum_s a[s] x_s;  out = u * rsqrt(mean(u^2) + eps) * (offset + w)
+//     write:  x_t <- sum_s m[s, t] x_s + b[t] y   for all t at once from the old streams (m indexed [from, to]),
+//             optionally followed by the read of the sublayer that runs next (its a, w), in the same kernel: the
+//             row's new streams are still in registers.
+// a, b, m are float32 (a null a reads the plain sum of the streams).  One CTA a token row; a thread holds the S values
+// of its columns in registers, S <= HYPER_MAX_STREAMS.  With `rows` the read kernel takes only the listed rows.
+#define HYPER_MAX_STREAMS 8
+
+template <typename TA, int S>
+__global__ void __launch_bounds__(256)
+hyper_read_norm_kernel(const float* __restrict__ streams, const float* __restrict__ a, const int* __restrict__ rows,
+                       const void* __restrict__ w, int w_dtype, float eps, float offset, TA* __restrict__ out, int H) {
+    extern __shared__ float hyper_smem[];                  // H floats, then 33 for the sum
+    float* scratch = hyper_smem + H;
+    pdl_wait();
+    const size_t t = rows ? (size_t)rows[blockIdx.x] : (size_t)blockIdx.x;
+    const float* x = streams + t * S * H;
+    float coef[S];
+#pragma unroll
+    for (int s = 0; s < S; ++s) coef[s] = a ? a[s] : 1.0f;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+        float u = 0.f;
+#pragma unroll
+        for (int s = 0; s < S; ++s) u = fmaf(coef[s], x[(size_t)s * H + i], u);
+        hyper_smem[i] = u;
+        ss = fmaf(u, u, ss);
+    }
+    ss = block_sum(ss, scratch);
+    pdl_trigger_late();
+    const float rstd = 1.0f / sqrtf(ss / (float)H + eps);
+    for (int i = threadIdx.x; i < H; i += blockDim.x)
+        out[(size_t)blockIdx.x * H + i] = from_f32<TA>(hyper_smem[i] * rstd * (offset + load_as_f32(w, w_dtype, i)));
+}
+
+template <typename TA, typename TY, int S>
+__global__ void __launch_bounds__(256)
+hyper_write_kernel(float* __restrict__ streams, const TY* __restrict__ y, const float* __restrict__ m,
+                   const float* __restrict__ b, const float* __restrict__ a_next, const void* __restrict__ w_next,
+                   int w_dtype, float eps, float offset, TA* __restrict__ out, int H) {
+    extern __shared__ float hyper_smem[];
+    float* scratch = hyper_smem + H;
+    pdl_wait();
+    const size_t t = blockIdx.x;
+    float* x = streams + t * S * H;
+    float mix[S][S], bo[S], an[S];
+#pragma unroll
+    for (int s = 0; s < S; ++s) {
+        bo[s] = b[s];
+        an[s] = out ? (a_next ? a_next[s] : 1.0f) : 0.f;
+#pragma unroll
+        for (int r = 0; r < S; ++r) mix[s][r] = m[s * S + r];
+    }
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+        float old[S];
+#pragma unroll
+        for (int s = 0; s < S; ++s) old[s] = x[(size_t)s * H + i];
+        const float yv = to_f32(y[t * H + i]);
+        float u = 0.f;
+#pragma unroll
+        for (int r = 0; r < S; ++r) {
+            float v = bo[r] * yv;
+#pragma unroll
+            for (int s = 0; s < S; ++s) v = fmaf(mix[s][r], old[s], v);
+            x[(size_t)r * H + i] = v;
+            u = fmaf(an[r], v, u);
+        }
+        if (out) {
+            hyper_smem[i] = u;
+            ss = fmaf(u, u, ss);
+        }
+    }
+    if (!out) return;
+    ss = block_sum(ss, scratch);
+    pdl_trigger_late();
+    const float rstd = 1.0f / sqrtf(ss / (float)H + eps);
+    for (int i = threadIdx.x; i < H; i += blockDim.x)
+        out[t * H + i] = from_f32<TA>(hyper_smem[i] * rstd * (offset + load_as_f32(w_next, w_dtype, i)));
+}
+
+template <typename TA, int S>
+static int hyper_read_launch(const float* streams, const float* a, const int* rows, const void* w, int w_dtype, float eps,
+                             float offset, void* out, int n, int H, cudaStream_t st) {
+    const size_t smem = (size_t)(H + 33) * sizeof(float);
+    return rb_launch_pdl(hyper_read_norm_kernel<TA, S>, dim3(n), dim3(256), smem, st, streams, a, rows, w, w_dtype, eps, offset,
+                         (TA*)out, H);
+}
+
+template <typename TA, typename TY, int S>
+static int hyper_write_launch(float* streams, const void* y, const float* m, const float* b, const float* a_next,
+                              const void* w_next, int w_dtype, float eps, float offset, void* out, int T, int H,
+                              cudaStream_t st) {
+    const size_t smem = (size_t)(H + 33) * sizeof(float);
+    return rb_launch_pdl(hyper_write_kernel<TA, TY, S>, dim3(T), dim3(256), smem, st, streams, (const TY*)y, m, b, a_next, w_next,
+                         w_dtype, eps, offset, (TA*)out, H);
+}
+
+#define HYPER_BY_STREAMS(CALL)                                                   \
+    switch (S) {                                                                 \
+        case 1: return CALL(1); case 2: return CALL(2); case 3: return CALL(3); \
+        case 4: return CALL(4); case 5: return CALL(5); case 6: return CALL(6); \
+        case 7: return CALL(7); case 8: return CALL(8);                          \
+        default: return (int)cudaErrorInvalidValue;                              \
+    }
+
+RB_EXPORT int rb_hyper_read_norm(const float* streams, const float* a, const int* rows, const void* w, int w_dtype, float eps,
+                                 float offset, void* out, int act_dtype, int n, int S, int H, cudaStream_t st) {
+    if (n <= 0) return 0;
+    if ((size_t)(H + 33) * sizeof(float) > 48 * 1024) return (int)cudaErrorInvalidValue;
+    if (act_dtype == RB_F32) {
+#define CALL(N) hyper_read_launch<float, N>(streams, a, rows, w, w_dtype, eps, offset, out, n, H, st)
+        HYPER_BY_STREAMS(CALL)
+#undef CALL
+    }
+#define CALL(N) hyper_read_launch<bf16, N>(streams, a, rows, w, w_dtype, eps, offset, out, n, H, st)
+    HYPER_BY_STREAMS(CALL)
+#undef CALL
+}
+
+RB_EXPORT int rb_hyper_write(float* streams, const void* y, int y_f32, const float* m, const float* b, const float* a_next,
+                             const void* w_next, int w_dtype, float eps, float offset, void* out, int act_dtype, int T,
+                             int S, int H, cudaStream_t st) {
+    if (T <= 0) return 0;
+    if ((size_t)(H + 33) * sizeof(float) > 48 * 1024) return (int)cudaErrorInvalidValue;
+    if (act_dtype == RB_F32) {                             // the 32-bit path: y is float32 as well
+#define CALL(N) hyper_write_launch<float, float, N>(streams, y, m, b, a_next, w_next, w_dtype, eps, offset, out, T, H, st)
+        HYPER_BY_STREAMS(CALL)
+#undef CALL
+    }
+    if (y_f32) {
+#define CALL(N) hyper_write_launch<bf16, float, N>(streams, y, m, b, a_next, w_next, w_dtype, eps, offset, out, T, H, st)
+        HYPER_BY_STREAMS(CALL)
+#undef CALL
+    }
+#define CALL(N) hyper_write_launch<bf16, bf16, N>(streams, y, m, b, a_next, w_next, w_dtype, eps, offset, out, T, H, st)
+    HYPER_BY_STREAMS(CALL)
+#undef CALL
 }

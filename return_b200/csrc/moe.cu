@@ -7,9 +7,10 @@
 #include "common.cuh"
 
 // ---------------------------------------------------------------- the router's choice
-// One warp a token.  s = softmax(z) over all experts (float32).  With groups > 1 the experts form `groups` equal
+// One warp a token.  s = softmax(z + bias) over all experts (float32; the bias per expert may be absent).  With groups > 1 the experts form `groups` equal
 // runs of neighbours, a group's score is its largest s, and only experts of the `keep` best groups can be chosen.
-// The `top` largest s among those are chosen (the lower index on a tie); weight = s / (sum of the chosen s + tiny).
+// The `top` largest s among those are chosen (the lower index on a tie); weight = s / (sum of the chosen s + tiny),
+// which with tiny = 0 is the softmax over the chosen logits alone.
 __device__ __forceinline__ void warp_argmax(float& v, int& i) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
@@ -20,8 +21,8 @@ __device__ __forceinline__ void warp_argmax(float& v, int& i) {
 }
 
 __global__ void __launch_bounds__(128)
-moe_route_kernel(const float* __restrict__ z, int ldz, int* __restrict__ expert_of, float* __restrict__ weight, int T, int E,
-                 int top, int groups, int keep, float tiny) {
+moe_route_kernel(const float* __restrict__ z, int ldz, const float* __restrict__ bias, int* __restrict__ expert_of,
+                 float* __restrict__ weight, int T, int E, int top, int groups, int keep, float tiny) {
     extern __shared__ float route_smem[];                 // per warp: E scores, then `groups` group scores
     pdl_launch_dependents();
     pdl_wait();
@@ -32,11 +33,15 @@ moe_route_kernel(const float* __restrict__ z, int ldz, int* __restrict__ expert_
     float* gs = s + E;
     const float* zr = z + (size_t)t * ldz;
     float m = -INFINITY;
-    for (int e = lane; e < E; e += 32) m = fmaxf(m, zr[e]);
+    for (int e = lane; e < E; e += 32) {
+        const float v = zr[e] + (bias ? bias[e] : 0.f);    // the logit with its bias waits in s[e] for the second pass
+        s[e] = v;
+        m = fmaxf(m, v);
+    }
     m = warp_max(m);
     float sum = 0.f;
     for (int e = lane; e < E; e += 32) {
-        const float v = expf(zr[e] - m);
+        const float v = expf(s[e] - m);
         s[e] = v;
         sum += v;
     }
@@ -86,14 +91,14 @@ moe_route_kernel(const float* __restrict__ z, int ldz, int* __restrict__ expert_
     for (int k = lane; k < top; k += 32) weight[(size_t)t * top + k] *= scale;
 }
 
-RB_EXPORT int rb_moe_route(const float* z, int ldz, int* expert_of, float* weight, int T, int E, int top, int groups, int keep,
-                           float tiny, cudaStream_t st) {
+RB_EXPORT int rb_moe_route(const float* z, int ldz, const float* bias, int* expert_of, float* weight, int T, int E, int top,
+                           int groups, int keep, float tiny, cudaStream_t st) {
     if (T <= 0) return 0;
     if (groups < 1 || E % groups || top < 1 || top > E || keep < 1 || keep > groups || (long long)keep * (E / groups) < top)
         return (int)cudaErrorInvalidValue;
     const size_t smem = (size_t)4 * (E + groups) * sizeof(float);
     if (smem > 48 * 1024) return (int)cudaErrorInvalidValue;
-    return rb_launch_pdl(moe_route_kernel, dim3((T + 3) / 4), dim3(128), smem, st, z, ldz, expert_of, weight, T, E, top,
+    return rb_launch_pdl(moe_route_kernel, dim3((T + 3) / 4), dim3(128), smem, st, z, ldz, bias, expert_of, weight, T, E, top,
                          groups, keep, tiny);
 }
 
@@ -201,10 +206,11 @@ RB_EXPORT int rb_moe_pair_linear(const void* x, int ldx, int in_div, const void*
 
 // ---------------------------------------------------------------- the gated unit with a capped gate
 // in[r] = [gate (F numbers) | up (F numbers)];  g = min(gate, limit), u = clamp(up, -limit, limit);
-// out[r, f] = g * sigmoid(alpha * g) * (u + 1).  float32 arithmetic, one rounding at the store.
+// out[r, f] = g * sigmoid(alpha * g) * (u + shift).  float32 arithmetic, one rounding at the store.  An infinite limit,
+// alpha = 1 and shift = 0 make it silu(gate) * up.
 template <typename TA>
 __global__ void clamped_glu_kernel(const TA* __restrict__ in, int ldi, TA* __restrict__ out, int ldo, int F, float limit,
-                                   float alpha, long long total) {
+                                   float alpha, float shift, long long total) {
     pdl_launch_dependents();
     pdl_wait();
     for (long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += (long long)gridDim.x * blockDim.x) {
@@ -212,13 +218,13 @@ __global__ void clamped_glu_kernel(const TA* __restrict__ in, int ldi, TA* __res
         const int f = (int)(e % F);
         const float g = fminf(to_f32(in[r * ldi + f]), limit);
         const float u = fminf(fmaxf(to_f32(in[r * ldi + F + f]), -limit), limit);
-        out[r * ldo + f] = from_f32<TA>(g / (1.0f + expf(-alpha * g)) * (u + 1.0f));
+        out[r * ldo + f] = from_f32<TA>(g / (1.0f + expf(-alpha * g)) * (u + shift));
     }
 }
 
 // bfloat16 with F a multiple of 8: eight outputs (two 16-byte loads, one store) a thread and step.
 __global__ void clamped_glu_bf16x8_kernel(const bf16* __restrict__ in, int ldi, bf16* __restrict__ out, int ldo, int F8,
-                                          float limit, float alpha, unsigned total) {
+                                          float limit, float alpha, float shift, unsigned total) {
     pdl_launch_dependents();
     pdl_wait();
     for (unsigned e = blockIdx.x * blockDim.x + threadIdx.x; e < total; e += gridDim.x * blockDim.x) {
@@ -233,14 +239,14 @@ __global__ void clamped_glu_bf16x8_kernel(const bf16* __restrict__ in, int ldi, 
         for (int k = 0; k < 8; ++k) {
             const float g = fminf(__bfloat162float(g8[k]), limit);
             const float u = fminf(fmaxf(__bfloat162float(u8[k]), -limit), limit);
-            o8[k] = __float2bfloat16_rn(g / (1.0f + expf(-alpha * g)) * (u + 1.0f));
+            o8[k] = __float2bfloat16_rn(g / (1.0f + expf(-alpha * g)) * (u + shift));
         }
         *reinterpret_cast<uint4*>(out + (size_t)r * ldo + f) = ov;
     }
 }
 
 RB_EXPORT int rb_clamped_glu(const void* in, int ldi, void* out, int ldo, int act_dtype, int rows, int F, float limit,
-                             float alpha, cudaStream_t st) {
+                             float alpha, float shift, cudaStream_t st) {
     const long long total = (long long)rows * F;
     if (total <= 0) return 0;
     if (act_dtype == RB_BF16 && F % 8 == 0 && ldi % 8 == 0 && ldo % 8 == 0 && ((uintptr_t)in % 16) == 0 &&
@@ -248,14 +254,14 @@ RB_EXPORT int rb_clamped_glu(const void* in, int ldi, void* out, int ldo, int ac
         const unsigned items = (unsigned)(total / 8);
         const int nblocks = (int)min((unsigned)(148 * 16), (items + 255) / 256);
         return rb_launch_pdl(clamped_glu_bf16x8_kernel, dim3(nblocks), dim3(256), 0, st, (const bf16*)in, ldi, (bf16*)out, ldo,
-                             F / 8, limit, alpha, items);
+                             F / 8, limit, alpha, shift, items);
     }
     const int blocks = (int)min((long long)4096, (total + 255) / 256);
     if (act_dtype == RB_F32)
         return rb_launch_pdl(clamped_glu_kernel<float>, dim3(blocks), dim3(256), 0, st, (const float*)in, ldi, (float*)out, ldo, F,
-                             limit, alpha, total);
+                             limit, alpha, shift, total);
     return rb_launch_pdl(clamped_glu_kernel<bf16>, dim3(blocks), dim3(256), 0, st, (const bf16*)in, ldi, (bf16*)out, ldo, F, limit,
-                         alpha, total);
+                         alpha, shift, total);
 }
 
 // ---------------------------------------------------------------- the weighted sum of a token's experts

@@ -7,6 +7,11 @@
 //     delta rule:      S <- g * S (row i by g_i);  u = beta (v - S^T k);  S <- S + k u^T;  o = S^T q
 //     matrix memory:   m' = max(f + m, i);  a = exp(f + m - m'),  b = exp(i - m');
 //                      S <- a S + b k v^T;  n <- a n + b k;  o = S^T q / (max(|n . q|, exp(-m')) + 1e-6)
+//     bonus rule:      o = (S + diag(u) k v^T)^T q;  S <- g * S (row i by g_i) + k v^T: the token's own pair is read with
+//                      a weight u per head and key row before the state takes it in (time mixing with a decay per token
+//                      and key row)
+//     state space:     S <- a S + dt k v^T;  o = S^T q + d v, with a decay a and a step dt per token and head and a
+//                      skip weight d per head (k and q are the input and output maps of a group of heads)
 // All of it is float32 whatever the activation type is.  The scan kernel walks the tokens of a segment in order,
 // one after the other, for prompts and single tokens alike: a token's result therefore does not depend on how a
 // prompt was cut into steps or on what else is in the batch (the sums have one fixed order).
@@ -28,13 +33,17 @@
 #define MODE_DECAY 0
 #define MODE_MEMORY 1
 #define MODE_DELTA 2
+#define MODE_BONUS 3
+#define MODE_SSM 4
 
 struct ScanArgs {
     const void* q; const void* k; const void* v;        // (t, head, i) at base + t * ld + head * dim + i
     int q_ld, k_ld, v_ld;
     int q_f32, k_f32, v_f32;                            // 1: float32, 0: bfloat16
-    const float* gate_a;      // decay: [H] decays; memory: [T, 2H] gate pre-activations (input, forget); delta: [T, H*D] row decays
-    const float* gate_b;      // memory: [2H] gate biases; delta: [T, H] beta
+    const float* gate_a;      // decay: [H] decays; memory: [T, 2H] gate pre-activations (input, forget); delta and bonus:
+                              // [T, H*D] row decays; state space: [T, H] decays
+    const float* gate_b;      // memory: [2H] gate biases; delta: [T, H] beta; state space: [T, H] steps
+    const float* extra;       // bonus: [H, D] weights of the token's own pair; state space: [H] skip weights
     float cap, q_scale;
     float* state;             // [slots, state_stride]
     long long state_stride;
@@ -70,11 +79,12 @@ linear_scan_kernel(const ScanArgs a) {
     // NR values as 16-byte pieces, and the eight runs that one such request covers fall on different banks
     constexpr int RS = NR + 4, DS = R * RS;
     constexpr int PER = SCAN_TC * DP / SCAN_THREADS;   // q (and k) elements of a chunk that a thread brings in
+    constexpr bool ROW_DECAY = MODE == MODE_DELTA || MODE == MODE_BONUS;     // a decay per token, head and key row
     static_assert(SCAN_TC * SCAN_COLS <= SCAN_THREADS && (SCAN_TC * DP) % SCAN_THREADS == 0, "staging by all threads");
     pdl_wait();
     __shared__ __align__(16) float sq[SCAN_TC][DS];
     __shared__ __align__(16) float sk[SCAN_TC][DS];
-    __shared__ __align__(16) float sg[MODE == MODE_DELTA ? SCAN_TC : 1][DS];
+    __shared__ __align__(16) float sg[ROW_DECAY ? SCAN_TC : 1][DS];
     __shared__ float sv[SCAN_TC][SCAN_COLS];
     __shared__ float sa[SCAN_TC], sb[SCAN_TC];
     const int seg = blockIdx.z, h = blockIdx.y, j0 = blockIdx.x * SCAN_COLS;
@@ -104,6 +114,15 @@ linear_scan_kernel(const ScanArgs a) {
         m = st[a.m_off + h];
     }
     const float decay = MODE == MODE_DECAY ? a.gate_a[h] : 0.f;
+    const float skip = MODE == MODE_SSM ? a.extra[h] : 0.f;
+    float bonus[MODE == MODE_BONUS ? NR : 1];
+    if (MODE == MODE_BONUS) {
+#pragma unroll
+        for (int ii = 0; ii < NR; ++ii) {
+            const int row = r + R * ii;
+            bonus[ii] = row < D ? a.extra[(size_t)h * D + row] : 0.f;
+        }
+    }
     const float bias_i = MODE == MODE_MEMORY ? a.gate_b[h] : 0.f, bias_f = MODE == MODE_MEMORY ? a.gate_b[H + h] : 0.f;
 
     // A chunk of up to SCAN_TC tokens comes from global memory into registers while the chunk before it is worked on,
@@ -111,7 +130,7 @@ linear_scan_kernel(const ScanArgs a) {
     // product right behind a load would make the warp wait for it there, before the arithmetic it is meant to hide
     // behind.  Converting, scaling and the gates' transcendental functions happen on the way to shared memory.
     uint32_t rq[PER], rk[PER], rv = 0u;
-    float rg[MODE == MODE_DELTA ? PER : 1], ra = 0.f, rb = 0.f;
+    float rg[ROW_DECAY ? PER : 1], ra = 0.f, rb = 0.f;
     auto raw = [](const void* p, int f32, size_t i) -> uint32_t {
         return f32 ? ((const uint32_t*)p)[i] : (uint32_t)((const unsigned short*)p)[i];
     };
@@ -125,7 +144,7 @@ linear_scan_kernel(const ScanArgs a) {
             const bool live = tt < nt && i < D;
             rq[u] = live ? raw(a.q, a.q_f32, t * a.q_ld + (size_t)kvh * D + i) : 0u;
             rk[u] = live ? raw(a.k, a.k_f32, t * a.k_ld + (size_t)kvh * D + i) : 0u;
-            if (MODE == MODE_DELTA) rg[u] = live ? a.gate_a[(t * H + h) * D + i] : 1.f;
+            if (ROW_DECAY) rg[u] = live ? a.gate_a[(t * H + h) * D + i] : 1.f;
         }
         if (tid < SCAN_TC * SCAN_COLS) {
             const int tt = tid / SCAN_COLS, c = tid - tt * SCAN_COLS;
@@ -138,6 +157,9 @@ linear_scan_kernel(const ScanArgs a) {
                 rb = a.gate_a[t * 2 * H + H + h];
             } else if (MODE == MODE_DELTA) {
                 rb = a.gate_b[t * H + h];
+            } else if (MODE == MODE_SSM) {
+                ra = a.gate_a[t * H + h];
+                rb = a.gate_b[t * H + h];
             }
         }
     };
@@ -148,7 +170,7 @@ linear_scan_kernel(const ScanArgs a) {
             const int at = (i % R) * RS + i / R;
             sq[tt][at] = cooked(rq[u], a.q_f32) * a.q_scale;
             sk[tt][at] = cooked(rk[u], a.k_f32);
-            if (MODE == MODE_DELTA) sg[tt][at] = rg[u];
+            if (ROW_DECAY) sg[tt][at] = rg[u];
         }
         if (tid < SCAN_TC * SCAN_COLS) sv[tid / SCAN_COLS][tid % SCAN_COLS] = cooked(rv, a.v_f32);
         if (tid < SCAN_TC) {
@@ -156,6 +178,7 @@ linear_scan_kernel(const ScanArgs a) {
                 sa[tid] = a.cap * tanhf((ra + bias_i) / a.cap);
                 sb[tid] = logsigmoid_f(a.cap * tanhf((rb + bias_f) / a.cap));
             } else {
+                sa[tid] = ra;
                 sb[tid] = rb;
             }
         }
@@ -197,6 +220,23 @@ linear_scan_kernel(const ScanArgs a) {
                 n4[ii & 3] = fmaf(n[ii], qr[ii], n4[ii & 3]);
             }
             np[tt] = (n4[0] + n4[1]) + (n4[2] + n4[3]);
+        } else if (MODE == MODE_BONUS) {
+            float gr[NR];
+#pragma unroll
+            for (int i4 = 0; i4 < NR; i4 += 4) *(float4*)&gr[i4] = *(const float4*)&sg[tt][r * RS + i4];
+#pragma unroll
+            for (int ii = 0; ii < NR; ++ii) {
+                const float kv = kr[ii] * vj;
+                o4[ii & 3] = fmaf(fmaf(bonus[ii], kv, S[ii]), qr[ii], o4[ii & 3]);
+                S[ii] = fmaf(gr[ii], S[ii], kv);
+            }
+        } else if (MODE == MODE_SSM) {
+            const float fa = sa[tt], vdt = sb[tt] * vj;
+#pragma unroll
+            for (int ii = 0; ii < NR; ++ii) {
+                S[ii] = fmaf(fa, S[ii], kr[ii] * vdt);
+                o4[ii & 3] = fmaf(S[ii], qr[ii], o4[ii & 3]);
+            }
         } else {
 #pragma unroll
             for (int i4 = 0; i4 < NR; i4 += 4) {
@@ -222,6 +262,7 @@ linear_scan_kernel(const ScanArgs a) {
             const float nq = lanes_sum<R>(np[tt]);
             o = o / (fmaxf(fabsf(nq), floor_[tt]) + 1e-6f);
         }
+        if (MODE == MODE_SSM) o = fmaf(skip, sv[tt][jj], o);
         if (r == 0 && col) a.out[((size_t)t * H + h) * V + j] = o;
     };
 
@@ -285,21 +326,25 @@ static int launch_scan(const ScanArgs& a, int segments, cudaStream_t st) {
     return rb_launch_pdl(linear_scan_kernel<MODE, 32, R>, grid, dim3(SCAN_THREADS), 0, st, a);
 }
 
-// mode: 0 fixed decay, 1 matrix memory, 2 delta rule.  The arguments are those of ScanArgs, in its order.
+// mode: 0 fixed decay, 1 matrix memory, 2 delta rule, 3 bonus rule, 4 state space.  The arguments are those of
+// ScanArgs, in its order.
 RB_EXPORT int rb_linear_scan(int mode, const void* q, const void* k, const void* v, int q_ld, int k_ld, int v_ld,
-                             int q_f32, int k_f32, int v_f32, const float* gate_a, const float* gate_b, float cap,
+                             int q_f32, int k_f32, int v_f32, const float* gate_a, const float* gate_b,
+                             const float* extra, float cap,
                              float q_scale, float* state, long long state_stride, int s_off, int n_off, int m_off,
                              int f_off, const int* cu_q, const int* seg_slot, float* out, int H, int G, int D, int V,
                              int segments, cudaStream_t st) {
     ScanArgs a;
     a.q = q; a.k = k; a.v = v; a.q_ld = q_ld; a.k_ld = k_ld; a.v_ld = v_ld;
     a.q_f32 = q_f32; a.k_f32 = k_f32; a.v_f32 = v_f32;
-    a.gate_a = gate_a; a.gate_b = gate_b; a.cap = cap; a.q_scale = q_scale;
+    a.gate_a = gate_a; a.gate_b = gate_b; a.extra = extra; a.cap = cap; a.q_scale = q_scale;
     a.state = state; a.state_stride = state_stride; a.s_off = s_off; a.n_off = n_off; a.m_off = m_off; a.f_off = f_off;
     a.cu_q = cu_q; a.seg_slot = seg_slot; a.out = out; a.H = H; a.G = G; a.D = D; a.V = V;
     if (mode == MODE_DECAY) return launch_scan<MODE_DECAY>(a, segments, st);
     if (mode == MODE_MEMORY) return launch_scan<MODE_MEMORY>(a, segments, st);
     if (mode == MODE_DELTA) return launch_scan<MODE_DELTA>(a, segments, st);
+    if (mode == MODE_BONUS) return extra ? launch_scan<MODE_BONUS>(a, segments, st) : (int)cudaErrorInvalidValue;
+    if (mode == MODE_SSM) return extra && gate_b ? launch_scan<MODE_SSM>(a, segments, st) : (int)cudaErrorInvalidValue;
     return (int)cudaErrorInvalidValue;
 }
 
@@ -703,4 +748,136 @@ RB_EXPORT int rb_scaled_sum(const void* a, int a_f32, float s1, const void* b, i
     if (out_f32) rb_launch_pdl(scaled_sum_kernel<float>, dim3(blocks), dim3(256), 0, st, a, a_f32, s1, b, b_f32, s2, (float*)y, (size_t)n);
     else rb_launch_pdl(scaled_sum_kernel<bf16>, dim3(blocks), dim3(256), 0, st, a, a_f32, s1, b, b_f32, s2, (bf16*)y, (size_t)n);
     return rb_launch_status();
+}
+
+// ---------------------------------------------------------------- token shift: mixes of a token's input with its predecessor's
+// out[n, t, :] = x[t] + (x[t-1] - x[t]) * mu[n], n < N, where x[t-1] of a segment's first token is the request's kept
+// row (state + shift_off: the last input of the step before, zero for a new request).  Float32 arithmetic.
+template <typename TA>
+__global__ void __launch_bounds__(256)
+token_shift_mix_kernel(const TA* __restrict__ x, int ld, const void* __restrict__ mu, int mu_dtype, int N,
+                       const float* __restrict__ state, long long state_stride, int shift_off,
+                       const int* __restrict__ tok_seg, const int* __restrict__ cu_q, const int* __restrict__ seg_slot,
+                       TA* __restrict__ out, int T, int W) {
+    pdl_wait();
+    const int t = blockIdx.x;
+    const int seg = tok_seg[t];
+    const bool first = t == cu_q[seg];
+    const float* kept = state + (long long)seg_slot[seg] * state_stride + shift_off;
+    const TA* cur = x + (size_t)t * ld;
+    for (int i = threadIdx.x; i < W; i += blockDim.x) {
+        const float c = to_f32(cur[i]);
+        const float d = (first ? kept[i] : to_f32(x[(size_t)(t - 1) * ld + i])) - c;
+        for (int n = 0; n < N; ++n)
+            out[((size_t)n * T + t) * W + i] = from_f32<TA>(fmaf(d, load_as_f32(mu, mu_dtype, (size_t)n * W + i), c));
+    }
+}
+
+RB_EXPORT int rb_token_shift_mix(const void* x, int ld, const void* mu, int mu_dtype, int N, const float* state,
+                                 long long state_stride, int shift_off, const int* tok_seg, const int* cu_q,
+                                 const int* seg_slot, void* out, int act_dtype, int T, int W, cudaStream_t st) {
+    if (T <= 0 || N <= 0) return 0;
+    const int threads = W >= 1024 ? 256 : 128;
+    if (act_dtype == RB_F32)
+        return rb_launch_pdl(token_shift_mix_kernel<float>, dim3(T), dim3(threads), 0, st, (const float*)x, ld, mu, mu_dtype, N,
+                             state, state_stride, shift_off, tok_seg, cu_q, seg_slot, (float*)out, T, W);
+    return rb_launch_pdl(token_shift_mix_kernel<bf16>, dim3(T), dim3(threads), 0, st, (const bf16*)x, ld, mu, mu_dtype, N, state,
+                         state_stride, shift_off, tok_seg, cu_q, seg_slot, (bf16*)out, T, W);
+}
+
+// ---------------------------------------------------------------- what the state-space scan needs of a token
+// x: rows of a projection buffer; C channels from column c_off pass a short causal convolution over time (taps [C, K],
+// the last column is the current token's; what lies before the segment comes from the request's conv state, which
+// holds the K - 1 inputs before it, oldest first, and is zero for a new request), plus a bias per channel, then silu;
+// the results go to conv_out [T, C] in float32.  H step sizes from column dt_off:
+//     dt[t, h] = softplus(x[t, dt_off + h] + dt_bias[h]),   decay[t, h] = exp(-exp(A_log[h]) * dt[t, h]).
+// blockIdx.y < gridDim.y - 1: a run of 256 channels; the last: the steps and decays.
+template <typename TA>
+__global__ void __launch_bounds__(256)
+ssm_prep_kernel(const TA* __restrict__ x, int ld, int c_off, int C, const void* __restrict__ taps, const void* __restrict__ bias,
+                int taps_dtype, int K, const float* __restrict__ state, long long state_stride, int conv_off,
+                const int* __restrict__ tok_seg, const int* __restrict__ cu_q, const int* __restrict__ seg_slot,
+                float* __restrict__ conv_out, int dt_off, int H, const void* __restrict__ dt_bias,
+                const void* __restrict__ A_log, int vec_dtype, float* __restrict__ dt, float* __restrict__ decay) {
+    pdl_wait();
+    const int t = blockIdx.x;
+    if (blockIdx.y == gridDim.y - 1) {
+        for (int h = threadIdx.x; h < H; h += blockDim.x) {
+            const float step = softplus_f(to_f32(x[(size_t)t * ld + dt_off + h]) + load_as_f32(dt_bias, vec_dtype, h));
+            dt[(size_t)t * H + h] = step;
+            decay[(size_t)t * H + h] = expf(-expf(load_as_f32(A_log, vec_dtype, h)) * step);
+        }
+        return;
+    }
+    const int c = blockIdx.y * blockDim.x + threadIdx.x;
+    if (c >= C) return;
+    const int seg = tok_seg[t];
+    const int l = t - cu_q[seg];                          // tokens of this segment before t
+    const float* cs = state + (long long)seg_slot[seg] * state_stride + conv_off + (size_t)c * (K - 1);
+    float y = 0.f;
+    for (int jb = K - 1; jb >= 0; --jb) {                 // jb tokens back, oldest first
+        const float w = load_as_f32(taps, taps_dtype, (size_t)c * K + (K - 1 - jb));
+        const float xv = jb <= l ? to_f32(x[(size_t)(t - jb) * ld + c_off + c]) : cs[K - 1 - (jb - l)];
+        y = fmaf(w, xv, y);
+    }
+    y += load_as_f32(bias, taps_dtype, c);
+    conv_out[(size_t)t * C + c] = y / (1.0f + expf(-y));
+}
+
+RB_EXPORT int rb_ssm_prep(const void* x, int ld, int c_off, int C, const void* taps, const void* bias, int taps_dtype, int K,
+                          const float* state, long long state_stride, int conv_off, const int* tok_seg, const int* cu_q,
+                          const int* seg_slot, float* conv_out, int dt_off, int H, const void* dt_bias, const void* A_log,
+                          int vec_dtype, float* dt, float* decay, int act_dtype, int T, cudaStream_t st) {
+    if (T <= 0) return 0;
+    if (K < 1 || C <= 0) return (int)cudaErrorInvalidValue;
+    dim3 grid(T, (C + 255) / 256 + 1);
+    if (act_dtype == RB_F32)
+        return rb_launch_pdl(ssm_prep_kernel<float>, grid, dim3(256), 0, st, (const float*)x, ld, c_off, C, taps, bias, taps_dtype, K,
+                             state, state_stride, conv_off, tok_seg, cu_q, seg_slot, conv_out, dt_off, H, dt_bias, A_log,
+                             vec_dtype, dt, decay);
+    return rb_launch_pdl(ssm_prep_kernel<bf16>, grid, dim3(256), 0, st, (const bf16*)x, ld, c_off, C, taps, bias, taps_dtype, K, state,
+                         state_stride, conv_off, tok_seg, cu_q, seg_slot, conv_out, dt_off, H, dt_bias, A_log, vec_dtype, dt,
+                         decay);
+}
+
+// ---------------------------------------------------------------- after the scan: gate first, then a norm over equal parts
+// v = y * silu(z); out[t, p, :] = v / sqrt(mean over the part (v^2) + eps) * w: a row of `width` values is normed in
+// `parts` equal parts, each by its own root mean square.  One warp a (token, part); the gate has the activation type
+// and rows of stride z_ld.
+template <typename TA>
+__global__ void gated_part_norm_kernel(const float* __restrict__ y, const TA* __restrict__ z, int z_ld,
+                                       const void* __restrict__ w, int w_dtype, float eps, TA* __restrict__ out, int rows,
+                                       int parts, int size) {
+    pdl_wait();
+    const int row = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+    if (row >= rows) return;
+    const int t = row / parts, p = row - t * parts;
+    const float* yr = y + (size_t)row * size;
+    const TA* zr = z + (size_t)t * z_ld + (size_t)p * size;
+    float ss = 0.f;
+    for (int i = lane; i < size; i += 32) {
+        const float g = to_f32(zr[i]);
+        const float v = yr[i] * (g / (1.0f + expf(-g)));
+        ss = fmaf(v, v, ss);
+    }
+    ss = warp_sum(ss);
+    const float rstd = 1.0f / sqrtf(ss / (float)size + eps);
+    TA* o = out + (size_t)row * size;
+    for (int i = lane; i < size; i += 32) {
+        const float g = to_f32(zr[i]);
+        const float v = yr[i] * (g / (1.0f + expf(-g)));
+        o[i] = from_f32<TA>(v * rstd * load_as_f32(w, w_dtype, (size_t)p * size + i));
+    }
+}
+
+RB_EXPORT int rb_gated_part_norm(const float* y, const void* z, int z_ld, const void* w, int w_dtype, float eps, void* out,
+                                 int act_dtype, int T, int parts, int size, cudaStream_t st) {
+    const int rows = T * parts;
+    if (rows <= 0) return 0;
+    const int blocks = (rows + 3) / 4;
+    if (act_dtype == RB_F32)
+        return rb_launch_pdl(gated_part_norm_kernel<float>, dim3(blocks), dim3(128), 0, st, y, (const float*)z, z_ld, w, w_dtype, eps,
+                             (float*)out, rows, parts, size);
+    return rb_launch_pdl(gated_part_norm_kernel<bf16>, dim3(blocks), dim3(128), 0, st, y, (const bf16*)z, z_ld, w, w_dtype, eps,
+                         (bf16*)out, rows, parts, size);
 }

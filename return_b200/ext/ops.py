@@ -78,7 +78,11 @@ def core() -> ctypes.CDLL:
     if _core is None:
         lib = build.load("return_core", _CORE_SOURCES, {"RB_PDL_MODE": PDL_MODE})
         P, I, F = c_void_p, c_int, c_float
-        lib.rb_embedding.argtypes = [P, I, P, P, I, I, I, P]
+        lib.rb_embedding.argtypes = [P, I, P, P, I, I, I, F, I, P]
+        L = ctypes.c_longlong
+        lib.rb_activation.argtypes = [P, L, I, P, L, I, I, P, I, I, I, P]
+        lib.rb_hyper_read_norm.argtypes = [P, P, P, P, I, F, F, P, I, I, I, I, P]
+        lib.rb_hyper_write.argtypes = [P, P, I, P, P, P, P, I, F, F, P, I, I, I, I, P]
         lib.rb_add_rmsnorm.argtypes = [P, P, P, P, I, F, F, P, I, I, I, P]
         lib.rb_rmsnorm_rows.argtypes = [P, P, I, F, F, P, I, I, I, P]
         lib.rb_rmsnorm_rows_ld.argtypes = [P, I, P, I, F, F, P, I, I, I, I, P]
@@ -99,7 +103,7 @@ def core() -> ctypes.CDLL:
         lib.rb_softcap.argtypes = [P, F, ctypes.c_longlong, P]
         for name in ("rb_embedding", "rb_add_rmsnorm", "rb_rmsnorm_rows", "rb_swiglu", "rb_gemm_f32",
                      "rb_qk_norm_rope_write", "rb_attention_simt", "rb_sample", "rb_argmax", "rb_postnorm_add_norm",
-                     "rb_softcap"):
+                     "rb_softcap", "rb_activation", "rb_hyper_read_norm", "rb_hyper_write"):
             getattr(lib, name).restype = c_int
         _core = lib
     return _core
@@ -126,13 +130,69 @@ def build_all():
 
 # ------------------------------------------------------------------------------- elementwise
 
-def embedding(table: torch.Tensor, tokens: torch.Tensor, stream_out: torch.Tensor) -> None:
-    """stream_out[t] = float32(table[tokens[t]]); tokens int32 [T], stream_out float32 [T, H]."""
-    T, H = stream_out.shape
+def embedding(table: torch.Tensor, tokens: torch.Tensor, stream_out: torch.Tensor, scale: float = 1.0) -> None:
+    """stream_out[t] = scale * float32(table[tokens[t]]); tokens int32 [T], stream_out float32 [T, H], or [T, S, H] for a
+    model that keeps S residual streams (all S start as the embedded token)."""
+    T, H = stream_out.shape[0], stream_out.shape[-1]
+    copies = stream_out.shape[1] if stream_out.dim() == 3 else 1
     assert tokens.dtype == torch.int32 and stream_out.dtype == torch.float32
     assert table.shape[1] == H and table.is_contiguous() and stream_out.is_contiguous()
     _check(core().rb_embedding(_ptr(table), dtype_code(table.dtype), _ptr(tokens), _ptr(stream_out),
-                               T, H, table.shape[0], _stream()), "embedding")
+                               T, H, table.shape[0], float(scale), copies, _stream()), "embedding")
+
+
+ACTIVATIONS = {"relu2": 0, "tanh": 1, "gelu_tanh": 2, "silu": 3, "neg_exp_exp": 4}
+
+
+def activation(x: torch.Tensor, out: torch.Tensor, kind: str, bias: Optional[torch.Tensor] = None) -> None:
+    """out = f(x) over 2-d views with unit stride along a row (in place when out is x): ``relu2`` max(x, 0)^2, ``tanh``,
+    ``gelu_tanh``, ``silu``, ``neg_exp_exp`` exp(-exp(x + bias)) with a bias per column.  float32 arithmetic."""
+    assert x.dim() == 2 and out.shape == x.shape and x.stride(1) == 1 and out.stride(1) == 1
+    if bias is not None:
+        assert kind == "neg_exp_exp" and bias.numel() == x.shape[1] and bias.is_contiguous()
+    _check(core().rb_activation(_ptr(x), x.stride(0), dtype_code(x.dtype), _ptr(out), out.stride(0), dtype_code(out.dtype),
+                                ACTIVATIONS[kind], _ptr(bias), dtype_code(bias.dtype) if bias is not None else F32,
+                                x.shape[0], x.shape[1], _stream()), "activation")
+
+
+HYPER_MAX_STREAMS = 8
+
+
+def hyper_read_norm(streams: torch.Tensor, read: Optional[torch.Tensor], weight: torch.Tensor, eps: float, out: torch.Tensor,
+                    rows: Optional[torch.Tensor] = None, offset: float = 0.0) -> None:
+    """out = rmsnorm(sum_s read[s] * streams[:, s]) * (offset + weight).  streams float32 [T, S, H]; read float32 [S] or
+    None for the plain sum of the streams; ``rows`` (int32) picks the token rows (out then has one row per entry)."""
+    T, S, H = streams.shape
+    n = T if rows is None else rows.numel()
+    assert streams.dtype == torch.float32 and streams.is_contiguous() and out.is_contiguous() and out.shape == (n, H)
+    assert weight.numel() == H and (read is None or (read.dtype == torch.float32 and read.numel() == S))
+    assert rows is None or rows.dtype == torch.int32
+    _check(core().rb_hyper_read_norm(_ptr(streams), _ptr(read), _ptr(rows), _ptr(weight), dtype_code(weight.dtype), eps, offset,
+                                     _ptr(out), dtype_code(out.dtype), n, S, H, _stream()), "hyper_read_norm")
+
+
+def hyper_write(streams: torch.Tensor, y: torch.Tensor, mix: torch.Tensor, write: torch.Tensor, nxt=None,
+                out: Optional[torch.Tensor] = None) -> None:
+    """streams[:, t] <- sum_s mix[s, t] * streams[:, s] + write[t] * y for all t at once, in place (streams float32
+    [T, S, H]; mix float32 [S, S] indexed [from, to]; write float32 [S]; y [T, H] float32 or the activation type).  With
+    ``nxt`` = (read or None, weight, eps, offset) and ``out``, the read of the sublayer that runs next is done on the
+    new streams in the same kernel: out = rmsnorm(sum_t read[t] * streams[:, t]) * (offset + weight)."""
+    T, S, H = streams.shape
+    assert streams.dtype == torch.float32 and streams.is_contiguous() and y.shape == (T, H) and y.is_contiguous()
+    assert mix.dtype == write.dtype == torch.float32 and mix.shape == (S, S) and mix.is_contiguous() and write.numel() == S
+    read, weight, eps, offset = nxt if nxt is not None else (None, None, 0.0, 0.0)
+    if out is not None:
+        assert weight is not None and weight.numel() == H and out.shape == (T, H) and out.is_contiguous()
+        assert read is None or (read.dtype == torch.float32 and read.numel() == S)
+        act = dtype_code(out.dtype)
+    else:
+        act = dtype_code(y.dtype)
+    assert act == F32 or y.dtype in (torch.float32, torch.bfloat16)
+    if act == F32:
+        assert y.dtype == torch.float32
+    _check(core().rb_hyper_write(_ptr(streams), _ptr(y), 1 if y.dtype == torch.float32 else 0, _ptr(mix), _ptr(write),
+                                 _ptr(read), _ptr(weight), dtype_code(weight.dtype) if weight is not None else F32, eps,
+                                 offset, _ptr(out), act, T, S, H, _stream()), "hyper_write")
 
 
 def add_rmsnorm(stream: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor, eps: float,
@@ -798,7 +858,7 @@ def paged_attention(qkv, k_pool, v_pool, batch, block_table, page_size, out, num
 
 _recurrent = None
 _RECURRENT_SOURCES = ["recurrent.cu"]
-SCAN_DECAY, SCAN_MEMORY, SCAN_DELTA = 0, 1, 2
+SCAN_DECAY, SCAN_MEMORY, SCAN_DELTA, SCAN_BONUS, SCAN_SSM = 0, 1, 2, 3, 4
 SCAN_MAX_KEY_DIM = 256
 
 
@@ -809,7 +869,10 @@ def recurrent_lib() -> ctypes.CDLL:
     if _recurrent is None:
         lib = build.load("return_recurrent", _RECURRENT_SOURCES, {"RB_PDL_MODE": PDL_MODE})
         P, I, F, L = c_void_p, c_int, c_float, ctypes.c_longlong
-        lib.rb_linear_scan.argtypes = [I, P, P, P, I, I, I, I, I, I, P, P, F, F, P, L, I, I, I, I, P, P, P, I, I, I, I, I, P]
+        lib.rb_linear_scan.argtypes = [I, P, P, P, I, I, I, I, I, I, P, P, P, F, F, P, L, I, I, I, I, P, P, P, I, I, I, I, I, P]
+        lib.rb_token_shift_mix.argtypes = [P, I, P, I, I, P, L, I, P, P, P, P, I, I, I, P]
+        lib.rb_ssm_prep.argtypes = [P, I, I, I, P, P, I, I, P, L, I, P, P, P, P, I, I, P, P, I, P, P, I, I, P]
+        lib.rb_gated_part_norm.argtypes = [P, P, I, P, I, F, P, I, I, I, I, P]
         lib.rb_rotary_to_f32.argtypes = [P, I, I, I, P, P, I, P, P, P, I, I, I, I, F, F, P]
         lib.rb_scan_pieces_combine.argtypes = [P, L, P, L, I, P, P, P, P, I, I, I, P]
         lib.rb_scan_pieces_combine.restype = c_int
@@ -823,7 +886,8 @@ def recurrent_lib() -> ctypes.CDLL:
         lib.rb_add_dual_norm.argtypes = [P, P, I, F, P, I, F, P, P, P, I, F, F, P, P, I, I, I, P]
         lib.rb_scaled_sum.argtypes = [P, I, F, P, I, F, P, I, L, P]
         for name in ("rb_linear_scan", "rb_rotary_to_f32", "rb_delta_prep", "rb_conv_state_update",
-                     "rb_head_norm_gate", "rb_add_dual_norm", "rb_scaled_sum"):
+                     "rb_head_norm_gate", "rb_add_dual_norm", "rb_scaled_sum", "rb_token_shift_mix", "rb_ssm_prep",
+                     "rb_gated_part_norm"):
             getattr(lib, name).restype = c_int
         _recurrent = lib
     return _recurrent
@@ -838,14 +902,17 @@ def _is_f32(t: torch.Tensor) -> int:
 
 
 def linear_scan(mode: int, q, k, v, gate_a, gate_b, state, offsets, batch, out, heads: int, kv_heads: int,
-                dim: int, vdim: int, q_scale: float = 1.0, cap: float = 0.0, forgot_offset: int = -1) -> None:
+                dim: int, vdim: int, q_scale: float = 1.0, cap: float = 0.0, forgot_offset: int = -1, extra=None) -> None:
     """The recurrence of a mixer with a [dim, vdim] state per head, over every segment of the step, token by token.
 
     q, k: [T, >= kv_heads * dim] views (float32 or bfloat16, unit stride along a row), v: [T, >= heads * vdim];
     ``state``: float32 [slots, n], the row of a segment is ``batch.seg_slot``; ``offsets`` = (S, n, m): where the
     matrix, the normaliser and the running maximum start inside a row (the last two for ``SCAN_MEMORY`` only).
     ``gate_a`` / ``gate_b`` by mode: SCAN_DECAY: [heads] decays / None; SCAN_MEMORY: [T, 2 heads] gate
-    pre-activations (input, forget) / [2 heads] biases; SCAN_DELTA: [T, heads, dim] row decays / [T, heads] beta.
+    pre-activations (input, forget) / [2 heads] biases; SCAN_DELTA: [T, heads, dim] row decays / [T, heads] beta;
+    SCAN_BONUS (o = (S + diag(u) k v^T)^T q, then S <- g * S + k v^T): [T, heads, dim] row decays / None, ``extra`` = u
+    [heads, dim]; SCAN_SSM (S <- a S + dt k v^T, o = S^T q + d v): [T, heads] decays / [T, heads] steps, ``extra`` = d
+    [heads].
     out: float32 [T, heads * vdim].  ``forgot_offset`` (SCAN_MEMORY): where in a row the sum of the segment's log forget
     gates is left per head, or -1."""
     assert state.dtype == torch.float32 and state.dim() == 2 and state.is_contiguous()
@@ -854,9 +921,12 @@ def linear_scan(mode: int, q, k, v, gate_a, gate_b, state, offsets, batch, out, 
     assert gate_a.dtype == torch.float32 and gate_a.is_contiguous()
     if gate_b is not None:
         assert gate_b.dtype == torch.float32 and gate_b.is_contiguous()
+    if mode in (SCAN_BONUS, SCAN_SSM):
+        assert extra is not None and extra.dtype == torch.float32 and extra.is_contiguous()
+        assert extra.numel() == (heads * dim if mode == SCAN_BONUS else heads)
     _check(recurrent_lib().rb_linear_scan(
         mode, _ptr(q), _ptr(k), _ptr(v), q.stride(0), k.stride(0), v.stride(0), _is_f32(q), _is_f32(k), _is_f32(v),
-        _ptr(gate_a), _ptr(gate_b), cap, q_scale, _ptr(state), state.stride(0), offsets[0], offsets[1], offsets[2],
+        _ptr(gate_a), _ptr(gate_b), _ptr(extra), cap, q_scale, _ptr(state), state.stride(0), offsets[0], offsets[1], offsets[2],
         forgot_offset, _ptr(batch.cu_q), _ptr(batch.seg_slot), _ptr(out), heads, kv_heads, dim, vdim, batch.num_segments, _stream()),
         "linear_scan")
 
@@ -933,6 +1003,49 @@ def conv_state_update(x, taps_count: int, state, conv_off: int, batch, channels:
     _check(recurrent_lib().rb_conv_state_update(_ptr(x), x.stride(0), taps_count, _ptr(state), state.stride(0), conv_off,
                                                 _ptr(batch.cu_q), _ptr(batch.seg_slot), dtype_code(x.dtype), channels,
                                                 batch.num_segments, _stream()), "conv_state_update")
+
+
+def token_shift_mix(x, mu, state, shift_off: int, batch, out) -> None:
+    """out[n, t] = x[t] + (x[t - 1] - x[t]) * mu[n] for each of the N rows of ``mu`` [N, W]; the predecessor of a segment's
+    first token is the row the request kept (``state`` row of its slot from ``shift_off``; zero for a new request).
+    x [T, W] with unit stride along a row; out [N, T, W] of x's type."""
+    T, W = x.shape
+    N = mu.shape[0]
+    assert x.stride(1) == 1 and mu.is_contiguous() and mu.shape[1] == W and out.shape == (N, T, W) and out.is_contiguous()
+    assert out.dtype == x.dtype and state.dtype == torch.float32
+    _check(recurrent_lib().rb_token_shift_mix(_ptr(x), x.stride(0), _ptr(mu), dtype_code(mu.dtype), N, _ptr(state),
+                                              state.stride(0), shift_off, _ptr(batch.tok_seg), _ptr(batch.cu_q),
+                                              _ptr(batch.seg_slot), _ptr(out), dtype_code(x.dtype), T, W, _stream()),
+           "token_shift_mix")
+
+
+def ssm_prep(x, c_off: int, channels: int, taps, bias, state, conv_off: int, batch, conv_out, dt_off: int, heads: int,
+             dt_bias, A_log, dt, decay) -> None:
+    """What a state-space scan needs of every token: ``channels`` columns of ``x`` from ``c_off`` through a causal
+    convolution (taps [channels, K], last column the token's own; before a segment the request's conv state), plus
+    ``bias``, then silu, into float32 conv_out [T, channels]; dt = softplus(x[:, dt_off + h] + dt_bias[h]) and
+    decay = exp(-exp(A_log[h]) dt), float32 [T, heads]."""
+    T = x.shape[0]
+    K = taps.shape[1]
+    assert x.stride(1) == 1 and taps.is_contiguous() and taps.shape[0] == channels and bias.numel() == channels
+    assert bias.dtype == taps.dtype and dt_bias.dtype == A_log.dtype and dt_bias.numel() == A_log.numel() == heads
+    for t, cols in ((conv_out, channels), (dt, heads), (decay, heads)):
+        assert t.dtype == torch.float32 and t.is_contiguous() and t.shape == (T, cols)
+    _check(recurrent_lib().rb_ssm_prep(
+        _ptr(x), x.stride(0), c_off, channels, _ptr(taps), _ptr(bias), dtype_code(taps.dtype), K, _ptr(state), state.stride(0),
+        conv_off, _ptr(batch.tok_seg), _ptr(batch.cu_q), _ptr(batch.seg_slot), _ptr(conv_out), dt_off, heads, _ptr(dt_bias),
+        _ptr(A_log), dtype_code(A_log.dtype), _ptr(dt), _ptr(decay), dtype_code(x.dtype), T, _stream()), "ssm_prep")
+
+
+def gated_part_norm(y, gate, weight, parts: int, eps: float, out) -> None:
+    """v = y * silu(gate); out = v / rms(v) * weight, the root mean square taken over each of ``parts`` equal parts of a
+    row.  y float32 [T, n]; gate: a view [T, n] of the activation type; weight [n]; out [T, n] of the activation type."""
+    T, n = y.shape
+    assert y.dtype == torch.float32 and y.is_contiguous() and out.is_contiguous() and out.shape == (T, n) and n % parts == 0
+    assert gate.stride(1) == 1 and gate.dtype == out.dtype and gate.shape == (T, n) and weight.numel() == n
+    _check(recurrent_lib().rb_gated_part_norm(_ptr(y), _ptr(gate), gate.stride(0), _ptr(weight), dtype_code(weight.dtype), eps,
+                                              _ptr(out), dtype_code(out.dtype), T, parts, n // parts, _stream()),
+           "gated_part_norm")
 
 
 def head_norm_gate(o, gate, weight, weight_mode: int, gate_act: int, eps: float, out, heads: int, vdim: int) -> None:
@@ -1153,9 +1266,9 @@ def moe_lib() -> ctypes.CDLL:
     if _moe is None:
         lib = build.load("return_moe", _MOE_SOURCES, {"RB_PDL_MODE": PDL_MODE})
         P, I, F = c_void_p, c_int, c_float
-        lib.rb_moe_route.argtypes = [P, I, P, P, I, I, I, I, I, F, P]
+        lib.rb_moe_route.argtypes = [P, I, P, P, P, I, I, I, I, I, F, P]
         lib.rb_moe_pair_linear.argtypes = [P, I, I, P, P, P, I, I, I, I, I, P]
-        lib.rb_clamped_glu.argtypes = [P, I, P, I, I, I, I, F, F, P]
+        lib.rb_clamped_glu.argtypes = [P, I, P, I, I, I, I, F, F, F, P]
         lib.rb_moe_combine.argtypes = [P, P, P, P, P, I, I, I, I, P]
         lib.rb_moe_sort.argtypes = [P, I, I, P, P, P, P]
         lib.rb_moe_grouped_gemm.argtypes = [P, I, P, I, P, P, I, P, I, I, I, I, P]
@@ -1167,16 +1280,19 @@ def moe_lib() -> ctypes.CDLL:
     return _moe
 
 
-def moe_route(logits, expert_of, weight, top: int, groups: int = 1, keep: int = 1, tiny: float = 1e-20) -> None:
-    """The router's choice per token from float32 logits [T, E]: softmax over all experts; with ``groups`` > 1 only the
+def moe_route(logits, expert_of, weight, top: int, groups: int = 1, keep: int = 1, tiny: float = 1e-20, bias=None) -> None:
+    """The router's choice per token from float32 logits [T, E] (plus ``bias``, float32 [E], if given): softmax over all
+    experts; with ``groups`` > 1 only the
     experts of the ``keep`` groups (equal runs of neighbours) with the largest best score can be chosen; the ``top``
     largest scores among them, in falling order, into expert_of (int32 [T, top]) with weight = score / (sum + tiny)."""
     T, E = logits.shape
     assert logits.dtype == torch.float32 and logits.stride(1) == 1
     assert expert_of.dtype == torch.int32 and expert_of.shape == (T, top) and expert_of.is_contiguous()
     assert weight.dtype == torch.float32 and weight.shape == (T, top) and weight.is_contiguous()
-    _check(moe_lib().rb_moe_route(_ptr(logits), logits.stride(0), _ptr(expert_of), _ptr(weight), T, E, top, groups, keep, tiny,
-                                  _stream()), "moe_route")
+    if bias is not None:
+        assert bias.dtype == torch.float32 and bias.numel() == E and bias.is_contiguous()
+    _check(moe_lib().rb_moe_route(_ptr(logits), logits.stride(0), _ptr(bias), _ptr(expert_of), _ptr(weight), T, E, top, groups,
+                                  keep, tiny, _stream()), "moe_route")
 
 
 def moe_pair_linear(x, in_div: int, w, expert_of, out) -> None:
@@ -1189,13 +1305,13 @@ def moe_pair_linear(x, in_div: int, w, expert_of, out) -> None:
                                         dtype_code(x.dtype), pairs, N, K, _stream()), "moe_pair_linear")
 
 
-def clamped_glu(gate_up, out, limit: float, alpha: float) -> None:
-    """gate_up [rows, 2F] = [gate | up]: out = g * sigmoid(alpha g) * (u + 1) with g = min(gate, limit) and
-    u = clamp(up, -limit, limit)."""
+def clamped_glu(gate_up, out, limit: float, alpha: float, shift: float = 1.0) -> None:
+    """gate_up [rows, 2F] = [gate | up]: out = g * sigmoid(alpha g) * (u + shift) with g = min(gate, limit) and
+    u = clamp(up, -limit, limit).  An infinite limit, alpha = 1 and shift = 0 give silu(gate) * up."""
     rows, F2 = gate_up.shape
     assert out.shape == (rows, F2 // 2) and out.dtype == gate_up.dtype and gate_up.stride(1) == 1 and out.stride(1) == 1
     _check(moe_lib().rb_clamped_glu(_ptr(gate_up), gate_up.stride(0), _ptr(out), out.stride(0), dtype_code(out.dtype), rows,
-                                    F2 // 2, float(limit), float(alpha), _stream()), "clamped_glu")
+                                    F2 // 2, float(limit), float(alpha), float(shift), _stream()), "clamped_glu")
 
 
 def moe_combine(y, weight, shared, out, row_of=None) -> None:
@@ -1274,8 +1390,10 @@ MOE_GROUPED_MIN_PAIRS = 64
 MOE_TC5_MIN_PAIRS = 1024
 
 
-def moe_experts(x, gate_up, down, expert_of, weight, shared, out, limit: float, alpha: float, ctx=None) -> None:
-    """out[t] = sum_k weight[t, k] * expert_{expert_of[t, k]}(x[t]) (+ shared[t]); gate_up [E, 2F, H], down [E, H, F]."""
+def moe_experts(x, gate_up, down, expert_of, weight, shared, out, limit: float, alpha: float, ctx=None,
+                shift: float = 1.0) -> None:
+    """out[t] = sum_k weight[t, k] * expert_{expert_of[t, k]}(x[t]) (+ shared[t]); gate_up [E, 2F, H], down [E, H, F];
+    an expert is down(g sigmoid(alpha g) (u + shift)) with the gate capped at ``limit`` and the up part clamped to it."""
     E, F2, H = gate_up.shape
     T, top = expert_of.shape
     pairs = T * top
@@ -1298,16 +1416,16 @@ def moe_experts(x, gate_up, down, expert_of, weight, shared, out, limit: float, 
             rows = buf("moe.pair_rows", (pairs, H))
             moe_gather_rows(x, pair_at, top, rows)
             moe_tc5_gemm(rows, gate_up, offsets, gu)
-            clamped_glu(gu, act, limit, alpha)
+            clamped_glu(gu, act, limit, alpha, shift)
             moe_tc5_gemm(act, down, offsets, y)
         else:
             moe_grouped_gemm(x, pair_at, top, gate_up, offsets, gu)
-            clamped_glu(gu, act, limit, alpha)
+            clamped_glu(gu, act, limit, alpha, shift)
             moe_grouped_gemm(act, None, 1, down, offsets, y)
         moe_combine(y, weight, shared, out, row_of=place_of)
         return
     moe_pair_linear(x, top, gate_up, expert_of, gu)
-    clamped_glu(gu, act, limit, alpha)
+    clamped_glu(gu, act, limit, alpha, shift)
     moe_pair_linear(act, 1, down, expert_of, y)
     moe_combine(y, weight, shared, out)
 

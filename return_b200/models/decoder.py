@@ -25,9 +25,16 @@ class DecoderModel:
         self._graph_safe = None
         self.env = env
         self.blocks = [BLOCKS.build(b, env) for b in spec.layers]
+        if spec.streams is not None:
+            loose = [i for i, b in enumerate(self.blocks) if not getattr(b, "takes_streams", False)]
+            if loose or spec.embedding_norm is not None:
+                raise ValueError(f"a model with {spec.streams} residual streams is made of blocks that take them "
+                                 f"(layers {loose} do not) and norms no embedding")
         self.final_norm = NORMS.build(spec.final_norm, env)
         self.embedding_norm = NORMS.build(spec.embedding_norm, env) if spec.embedding_norm is not None else None
         self.embed: Optional[torch.Tensor] = None
+        # for looking inside a step: called as after_block(schedule index, stream, pending delta) behind every block
+        self.after_block = None
         self.lm_head: Optional[torch.Tensor] = None
 
     # ------------------------------------------------------------------ parameters
@@ -100,8 +107,9 @@ class DecoderModel:
         T = batch.num_tokens
         H = self.spec.hidden_size
         dev = self.env.device
-        stream = torch.empty((T, H), dtype=torch.float32, device=dev)
-        ops.embedding(self.embed, batch.tokens, stream)
+        S = self.spec.streams
+        stream = torch.empty((T, H) if S is None else (T, S, H), dtype=torch.float32, device=dev)
+        ops.embedding(self.embed, batch.tokens, stream, self.spec.embedding_scale)
         if self.embedding_norm is not None:
             self.embedding_norm.forward(stream, stream)           # in place: a warp reads its row before it writes it
         delta = None
@@ -115,13 +123,19 @@ class DecoderModel:
             if isinstance(delta, tuple) and not getattr(block, "takes_delta_pair", False):
                 delta = self._fold(stream, delta)
             delta = block.forward(stream, delta, ctx)
+            if self.after_block is not None:
+                self.after_block(index, stream, delta)
         if isinstance(delta, tuple):
             delta = self._fold(stream, delta)
         n_want = batch.num_want
         logits = torch.empty((n_want, self.spec.vocab_size), dtype=torch.float32, device=dev)
         if n_want:
             hidden = torch.empty((n_want, H), dtype=self.env.act_dtype, device=dev)
-            self.final_norm.add_forward(stream, delta, hidden, rows=batch.want_rows)
+            if S is None:
+                self.final_norm.add_forward(stream, delta, hidden, rows=batch.want_rows)
+            else:                                  # the sum of the streams goes to the final norm
+                n = self.final_norm
+                ops.hyper_read_norm(stream, None, n.p_weight, n.spec.eps, hidden, rows=batch.want_rows, offset=n.spec.offset)
             ops.linear(hidden, self.lm_head, logits)
             if self.spec.logit_softcap is not None:
                 ops.softcap(logits, self.spec.logit_softcap)

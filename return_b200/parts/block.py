@@ -10,7 +10,7 @@ from __future__ import annotations
 import torch
 
 from ..ext import ops
-from .base import BLOCKS, FEED_FORWARDS, MIXERS, NORMS, Block
+from .base import BLOCKS, FEED_FORWARDS, MIXERS, NORMS, Block, ParamSpec
 
 
 @BLOCKS.register("prenorm")
@@ -283,4 +283,106 @@ class SandwichBlock(Block):
             held["sandwich.prenormed"] = {"rows": rows, "position": ctx.position + 1}
         else:
             ops.postnorm_add_norm(stream, last[0], self._triple(last[1]))
+        return None
+
+
+@BLOCKS.register("hyper")
+class HyperBlock(Block):
+    """A pre-norm layer over several residual streams (``HyperBlockSpec``).  The stream tensor is float32 [T, S, H].
+
+    Two kernels serve a sublayer (csrc/elementwise.cu): the read (the weighted sum of the streams, normed) and the write
+    (every stream becomes a mix of the old ones plus its share of the sublayer's output).  The write also does the read
+    of whatever runs next while the row's new streams are in registers: the feed-forward's, or, across the border, the
+    next block's first read when that block is of this kind (left under ``hyper.prenormed`` in the step's scratch)."""
+
+    takes_streams = True
+
+    def __init__(self, spec, env):
+        super().__init__(spec, env)
+        if not (1 <= spec.streams <= ops.HYPER_MAX_STREAMS):
+            raise ValueError(f"streams={spec.streams}: 1 to {ops.HYPER_MAX_STREAMS}")
+        self.mixer = MIXERS.build(spec.mixer, env)
+        self.feed_forward = FEED_FORWARDS.build(spec.feed_forward, env) if spec.feed_forward is not None else None
+        self._children = {"mixer": self.mixer, "mixer_norm": NORMS.build(spec.mixer_norm, env)}
+        if self.feed_forward is not None:
+            self._children.update({"feed_forward": self.feed_forward,
+                                   "feed_forward_norm": NORMS.build(spec.feed_forward_norm, env)})
+        for name, part in self._children.items():
+            if name.endswith("norm") and getattr(part.spec, "kind", None) != "rmsnorm":
+                raise ValueError("the norms of a hyper block are RMSNorms")
+        self._sublayers = ("mixer", "feed_forward") if self.feed_forward is not None else ("mixer",)
+
+    @property
+    def graph_safe(self):
+        return all(part.graph_safe for part in self._children.values())
+
+    def params(self):
+        S = self.spec.streams
+        p = {f"{child}.{name}": ps for child, part in self._children.items() for name, ps in part.params().items()}
+        for sub in self._sublayers:
+            p[f"{sub}_read"] = ParamSpec((S,), role="vector", init="ones_normal")
+            p[f"{sub}_write"] = ParamSpec((S,), role="vector", init="ones_normal")
+            p[f"{sub}_mix"] = ParamSpec((S, S), role="vector", init="normal:0.4")
+        return p
+
+    def bind(self, tensors):
+        for child, part in self._children.items():
+            prefix = child + "."
+            part.bind({k[len(prefix):]: v for k, v in tensors.items() if k.startswith(prefix)})
+        # the streams' arithmetic is float32 whatever the checkpoint stores
+        self.hc = {sub: tuple(tensors[f"{sub}_{n}"].float().contiguous() for n in ("read", "write", "mix"))
+                   for sub in self._sublayers}
+
+    def cache_need(self):
+        return self.mixer.cache_need()
+
+    def batch_tilings(self):
+        out = {}
+        for part in self._children.values():
+            out.update(part.batch_tilings())
+        return out
+
+    def graph_variant(self, n_tokens, longest_context):
+        out = {}
+        for part in self._children.values():
+            out.update(part.graph_variant(n_tokens, longest_context))
+        return out
+
+    def first_read(self):
+        """(read vector, norm weight, eps, offset) of this block's first sublayer: what the block before it needs to do
+        that read in its last write."""
+        n = self._children["mixer_norm"]
+        return self.hc["mixer"][0], n.p_weight, n.spec.eps, n.spec.offset
+
+    def forward(self, streams, delta, ctx):
+        if streams.dim() != 3 or streams.shape[1] != self.spec.streams:
+            raise ValueError(f"a hyper block of {self.spec.streams} streams was handed a stream tensor of shape {tuple(streams.shape)}")
+        if delta is not None:
+            raise ValueError("a hyper block takes no pending residual: the block before it must write the streams itself")
+        T, S, H = streams.shape
+        dt, dev = self.env.act_dtype, streams.device
+        c = self._children
+        held = getattr(ctx.batch, "scratch", None)
+        pre = held.pop("hyper.prenormed", None) if held is not None else None
+        if pre is not None and pre["position"] == ctx.position:
+            a = pre["rows"]                                     # the block before this one did this read in its last write
+        else:
+            a = ctx.buffer("hyper.read_a", (T, H), dt, dev)
+            n = c["mixer_norm"]
+            ops.hyper_read_norm(streams, self.hc["mixer"][0], n.p_weight, n.spec.eps, a, offset=n.spec.offset)
+        y = self.mixer.forward(a, ctx)
+        _, write, mix = self.hc["mixer"]
+        if self.feed_forward is not None:
+            n = c["feed_forward_norm"]
+            b = ctx.buffer("hyper.read_b", (T, H), dt, dev)
+            ops.hyper_write(streams, y, mix, write, nxt=(self.hc["feed_forward"][0], n.p_weight, n.spec.eps, n.spec.offset), out=b)
+            y = self.feed_forward.forward(b, ctx)
+            _, write, mix = self.hc["feed_forward"]
+        nxt = ctx.next_block
+        if held is not None and isinstance(nxt, HyperBlock) and nxt.spec.streams == S:
+            rows = ctx.buffer("hyper.read_a", (T, H), dt, dev)          # this block's own first read is used up by now
+            ops.hyper_write(streams, y, mix, write, nxt=nxt.first_read(), out=rows)
+            held["hyper.prenormed"] = {"rows": rows, "position": ctx.position + 1}
+        else:
+            ops.hyper_write(streams, y, mix, write)
         return None

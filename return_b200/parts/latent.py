@@ -174,7 +174,7 @@ class LatentAttention(Mixer):
             ops.linear(cq, self.p_uq, q)
         else:
             q = proj                                             # the queries are the first columns of the projection
-        cos, sin, _ = self.position.rotary_tables() if self.position is not None else (None, None, 0)
+        cos, sin, _ = self.position.tables() if self.position is not None else (None, None, 0)
         # a head's query as the attention reads it: [its unrotated part carried into the latent's space | its rotated part]
         q_abs = ctx.buffer("latent.q_abs", (T, H * W), dt, dev)
         ops.latent_write(proj, self.c_off, self.p_kv_norm_weight, s.eps, C, R, cos, sin, b, kv.block_table, kv.page_size,

@@ -36,3 +36,29 @@ class SwiGLU(FeedForward):
         y = work_buffer(ctx, "mlp.y", (T, s.hidden_size), x.dtype, x.device)
         ops.linear(act, self.p_down, y)
         return y
+
+
+@FEED_FORWARDS.register("dense_mlp")
+class DenseMLP(FeedForward):
+    """y = down( act(up(x)) ) without a gate (``DenseMLPSpec``); the activation is applied in place on the first
+    product's output, in float32 arithmetic."""
+
+    def __init__(self, spec, env):
+        super().__init__(spec, env)
+        if spec.activation not in ("relu2", "gelu_tanh", "silu"):
+            raise ValueError(f"activation={spec.activation!r}; known: relu2, gelu_tanh, silu")
+
+    def params(self):
+        s = self.spec
+        return {"up": ParamSpec((s.intermediate_size, s.hidden_size)),
+                "down": ParamSpec((s.hidden_size, s.intermediate_size))}
+
+    def forward(self, x, ctx):
+        s = self.spec
+        T = x.shape[0]
+        act = work_buffer(ctx, "dense_mlp.act", (T, s.intermediate_size), x.dtype, x.device)
+        ops.linear(x, self.p_up, act)
+        ops.activation(act, act, s.activation)
+        y = work_buffer(ctx, "dense_mlp.y", (T, s.hidden_size), x.dtype, x.device)
+        ops.linear(act, self.p_down, y)
+        return y

@@ -1,9 +1,11 @@
 """Feed-forwards with a capped gated unit, dense or as a mixture of experts.
 
 ``clamped_glu``: y = down( g * sigmoid(alpha g) * (u + 1) ), g = min(gate(x), limit), u = clamp(up(x), -limit, limit).
-``moe``: a router (float32 logits, softmax over all experts, optionally only the experts of the best groups, the top
-few chosen, their scores renormalised) picks experts per token; the experts' outputs are summed with those weights,
-in the order of falling score, and a shared feed-forward may run for every token beside them.
+``moe``: a router (float32 logits, optionally with a bias per expert, softmax over all experts, optionally only the
+experts of the best groups, the top few chosen, their scores renormalised) picks experts per token; the experts'
+outputs are summed with those weights, in the order of falling score, and a shared feed-forward may run for every token
+beside them.  The experts are capped gated units or plain ones (silu(gate) * up), which are the same kernel with no
+cap, alpha = 1 and nothing added to the up part.
 
 The experts' weights are stacked: ``experts.gate_up`` [E * 2F, hidden] (per expert its gate rows, then its up rows)
 and ``experts.down`` [E * hidden, F].  Everything from the router's choice on happens on the device with grids that
@@ -41,8 +43,13 @@ class MixtureOfExperts(FeedForward):
     def __init__(self, spec, env):
         super().__init__(spec, env)
         s = spec
-        if getattr(s.expert, "kind", None) != "clamped_glu":
-            raise ValueError("the experts of a mixture are capped gated units (kind 'clamped_glu')")
+        kind = getattr(s.expert, "kind", None)
+        if kind == "clamped_glu":
+            self.unit = (float(s.expert.limit), float(s.expert.alpha), 1.0)       # cap, alpha, what is added to the up part
+        elif kind == "swiglu" and not s.expert.interleave:
+            self.unit = (float("inf"), 1.0, 0.0)
+        else:
+            raise ValueError("the experts of a mixture are gated units: kind 'clamped_glu', or 'swiglu' with rows not woven")
         if s.expert.hidden_size != s.hidden_size:
             raise ValueError("an expert maps the model's width to itself")
         if s.groups < 1 or s.num_experts % s.groups or not (1 <= s.keep_groups <= s.groups):
@@ -58,6 +65,7 @@ class MixtureOfExperts(FeedForward):
     def params(self):
         s, e = self.spec, self.spec.expert
         p = {"router": ParamSpec((s.num_experts, s.hidden_size)),
+             **({"router_bias": ParamSpec((s.num_experts,), role="vector", init="normal:0.5")} if s.router_bias else {}),
              "experts.gate_up": ParamSpec((s.num_experts * 2 * e.intermediate_size, s.hidden_size)),
              "experts.down": ParamSpec((s.num_experts * s.hidden_size, e.intermediate_size))}
         if self.shared is not None:
@@ -68,6 +76,7 @@ class MixtureOfExperts(FeedForward):
     def bind(self, tensors):
         s, e = self.spec, self.spec.expert
         self.p_router = tensors["router"]
+        self.router_bias = tensors["router_bias"].float().contiguous() if s.router_bias else None
         self.gate_up = tensors["experts.gate_up"].view(s.num_experts, 2 * e.intermediate_size, s.hidden_size)
         self.down = tensors["experts.down"].view(s.num_experts, s.hidden_size, e.intermediate_size)
         if self.shared is not None:
@@ -80,8 +89,9 @@ class MixtureOfExperts(FeedForward):
         ops.linear(x, self.p_router, logits)
         expert_of = work_buffer(ctx, "moe.expert_of", (T, s.top), torch.int32, dev)
         weight = work_buffer(ctx, "moe.weight", (T, s.top), torch.float32, dev)
-        ops.moe_route(logits, expert_of, weight, s.top, s.groups, s.keep_groups, s.renorm_tiny)
+        ops.moe_route(logits, expert_of, weight, s.top, s.groups, s.keep_groups, s.renorm_tiny, bias=self.router_bias)
         shared = self.shared.forward(x, ctx) if self.shared is not None else None
         y = work_buffer(ctx, "moe.y", (T, s.hidden_size), dt, dev)
-        ops.moe_experts(x, self.gate_up, self.down, expert_of, weight, shared, y, e.limit, e.alpha, ctx)
+        limit, alpha, shift = self.unit
+        ops.moe_experts(x, self.gate_up, self.down, expert_of, weight, shared, y, limit, alpha, ctx, shift=shift)
         return y

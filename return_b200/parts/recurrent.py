@@ -252,3 +252,125 @@ class MatrixMemory(_StateMixer):
         mixed = ctx.buffer("matrix_memory.mixed", (T, HV), x.dtype, dev)
         ops.head_norm_gate(o, proj[:, 2 * HD + HV:], self.p_norm, 2, 1, s.eps, mixed, self.H, self.V)
         return self._project_out(mixed, ctx)
+
+
+@MIXERS.register("time_mix")
+class TimeMix(_StateMixer):
+    """``TimeMixSpec``: five projections of five blends of a token's input with its predecessor's, a decay per token,
+    head and key row through a low rank, the scan with a bonus for the token's own pair, per-head norm, gate, output
+    projection.  The request's state row holds S and then the last input it saw (zero for a new request)."""
+
+    def __init__(self, spec, env):
+        super().__init__(spec, env)
+        s = spec
+        self.H, self.D, self.V = s.num_heads, s.key_dim, s.key_dim
+        if self.D > ops.SCAN_MAX_KEY_DIM:
+            raise ValueError(f"key_dim={self.D}: the scan kernel holds up to {ops.SCAN_MAX_KEY_DIM} key rows a head")
+        if s.decay_rank <= 0:
+            raise ValueError("decay_rank must be positive")
+        self.s_floats = self.H * _pad8(self.D) * self.V
+        self.shift_off = self.s_floats
+
+    def params(self):
+        s = self.spec
+        W, HD = s.hidden_size, self.H * self.D
+        return {"mu": ParamSpec((5, W), role="vector", init="uniform01"),                  # rows: r, k, v, gate, decay
+                "r": ParamSpec((HD, W)), "k": ParamSpec((HD, W)), "v": ParamSpec((HD, W)), "g": ParamSpec((HD, W)),
+                "decay_down": ParamSpec((s.decay_rank, W)),
+                "decay_up": ParamSpec((HD, s.decay_rank), init="normal:0.2"),
+                "decay_bias": ParamSpec((HD,), role="vector", init="normal:0.5"),
+                "bonus": ParamSpec((self.H, self.D), role="vector", init="normal:0.5"),
+                "norm": ParamSpec((HD,), role="vector", init="ones_normal"),
+                "o": ParamSpec((s.hidden_size, HD))}
+
+    def bind(self, tensors):
+        super().bind(tensors)
+        self._bonus32 = self.p_bonus.float().contiguous()
+
+    def cache_need(self):
+        return StateNeed((self.s_floats + self.spec.hidden_size,), torch.float32)
+
+    def forward(self, x, ctx):
+        s, b = self.spec, ctx.batch
+        T, dev, dt = x.shape[0], x.device, x.dtype
+        W, HD = s.hidden_size, self.H * self.D
+        mixes = ctx.buffer("time_mix.mixes", (5, T, W), dt, dev)
+        ops.token_shift_mix(x, self.p_mu, ctx.state, self.shift_off, b, mixes)
+        ops.conv_state_update(x, 2, ctx.state, self.shift_off, b, W)           # the last input, after every token read the old one
+        proj = ctx.buffer("time_mix.rkvg", (4, T, HD), dt, dev)
+        for i, w in enumerate((self.p_r, self.p_k, self.p_v, self.p_g)):
+            ops.linear(mixes[i], w, proj[i])
+        low = ctx.buffer("time_mix.low", (T, s.decay_rank), dt, dev)
+        ops.linear(mixes[4], self.p_decay_down, low)
+        ops.activation(low, low, "tanh")
+        decay = ctx.buffer("time_mix.decay", (T, HD), torch.float32, dev)
+        ops.linear(low, self.p_decay_up, decay)
+        ops.activation(decay, decay, "neg_exp_exp", bias=self.p_decay_bias)
+        o = ctx.buffer("time_mix.o", (T, HD), torch.float32, dev)
+        ops.linear_scan(ops.SCAN_BONUS, proj[0], proj[1], proj[2], decay, None, ctx.state, (0, 0, 0), b, o,
+                        self.H, self.H, self.D, self.V, extra=self._bonus32)
+        mixed = ctx.buffer("time_mix.mixed", (T, HD), dt, dev)
+        ops.head_norm_gate(o, proj[3], self.p_norm, 2, 0, s.eps, mixed, self.H, self.V)
+        return self._project_out(mixed, ctx)
+
+
+@MIXERS.register("state_space")
+class StateSpace(_StateMixer):
+    """``StateSpaceSpec``: one projection, the convolution of its x, B and C channels, the scan with a scalar decay per
+    token and head, gate, norm over equal parts, output projection.  The request's state row holds S (the state size
+    as key rows, the head's values as columns) and then the last ``conv_taps - 1`` inputs of every convolved channel."""
+
+    def __init__(self, spec, env):
+        super().__init__(spec, env)
+        s = spec
+        self.H, self.D, self.V = s.num_heads, s.state_dim, s.value_dim
+        if self.D > ops.SCAN_MAX_KEY_DIM:
+            raise ValueError(f"state_dim={self.D}: the scan kernel holds up to {ops.SCAN_MAX_KEY_DIM} state rows a head")
+        if s.groups < 1 or s.num_heads % s.groups:
+            raise ValueError(f"num_heads={s.num_heads} is not a multiple of groups={s.groups}")
+        self.inner = self.H * self.V
+        if s.norm_groups < 1 or self.inner % s.norm_groups:
+            raise ValueError(f"{self.inner} values do not form {s.norm_groups} equal parts")
+        if not (1 <= s.conv_taps <= 33):
+            raise ValueError("conv_taps: 1 to 33")
+        self.GN = s.groups * self.D
+        self.channels = self.inner + 2 * self.GN
+        self.s_floats = self.H * _pad8(self.D) * self.V
+        self.conv_off = self.s_floats
+
+    def params(self):
+        s = self.spec
+        return {"in": ParamSpec((2 * self.inner + 2 * self.GN + self.H, s.hidden_size)),       # z, x, B, C, dt
+                "conv": ParamSpec((self.channels, s.conv_taps), role="vector", init="normal:0.5"),
+                "conv_bias": ParamSpec((self.channels,), role="vector", init="normal:0.2"),
+                "dt_bias": ParamSpec((self.H,), role="vector", init="normal:0.5"),
+                "A_log": ParamSpec((self.H,), role="vector", init="normal:0.5"),
+                "D": ParamSpec((self.H,), role="vector", init="ones_normal"),
+                "norm": ParamSpec((self.inner,), role="vector", init="ones_normal"),
+                "o": ParamSpec((s.hidden_size, self.inner))}
+
+    def bind(self, tensors):
+        super().bind(tensors)
+        self._skip32 = self.p_D.float().contiguous()
+
+    def cache_need(self):
+        return StateNeed((self.s_floats + self.channels * (self.spec.conv_taps - 1),), torch.float32)
+
+    def forward(self, x, ctx):
+        s, b = self.spec, ctx.batch
+        T, dev = x.shape[0], x.device
+        inner, GN, C = self.inner, self.GN, self.channels
+        proj = ctx.buffer("state_space.in", (T, 2 * inner + 2 * GN + self.H), x.dtype, dev)
+        ops.linear(x, self.p_in, proj)
+        conv = ctx.buffer("state_space.conv", (T, C), torch.float32, dev)
+        step = ctx.buffer("state_space.dt", (T, self.H), torch.float32, dev)
+        decay = ctx.buffer("state_space.decay", (T, self.H), torch.float32, dev)
+        ops.ssm_prep(proj, inner, C, self.p_conv, self.p_conv_bias, ctx.state, self.conv_off, b, conv, inner + C, self.H,
+                     self.p_dt_bias, self.p_A_log, step, decay)
+        ops.conv_state_update(proj[:, inner:], s.conv_taps, ctx.state, self.conv_off, b, C)   # after every token read the old one
+        y = ctx.buffer("state_space.y", (T, inner), torch.float32, dev)
+        ops.linear_scan(ops.SCAN_SSM, conv[:, inner + GN:], conv[:, inner:inner + GN], conv[:, :inner], decay, step, ctx.state,
+                        (0, 0, 0), b, y, self.H, s.groups, self.D, self.V, extra=self._skip32)
+        mixed = ctx.buffer("state_space.mixed", (T, inner), x.dtype, dev)
+        ops.gated_part_norm(y, proj[:, :inner], self.p_norm, s.norm_groups, s.eps, mixed)
+        return self._project_out(mixed, ctx)

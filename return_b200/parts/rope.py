@@ -123,6 +123,16 @@ class RampedRotaryEncoding(PositionEncoding):
         return f / factor * ramp + f * (1.0 - ramp), float(spec.magnitude_slope) * math.log(factor) + 1.0
 
     def rotary_tables(self):
+        """(cos, sin, rotary_dim) for the kernel that rotates while it writes the cache, which takes widths that are
+        multiples of 4; None for any other even width: the attention then calls ``apply``."""
+        return self.tables() if self.spec.rotary_dim % 4 == 0 else None
+
+    def apply(self, qkv, batch, num_heads, num_kv_heads, head_dim):
+        from ..ext import ops
+        cos, sin, rot = self.tables()
+        ops.rotary_inplace(qkv, cos, sin, rot, batch.pos, num_heads + num_kv_heads, head_dim)
+
+    def tables(self):
         """(cos, sin, rotary_dim); cos and sin are float32 [max_positions, rotary_dim/2] on the device, the factor
         already in them."""
         if self._tables is None:
@@ -136,8 +146,6 @@ class RampedRotaryEncoding(PositionEncoding):
                                          (ang.sin() * mag).float().contiguous().to(self.env.device), s.rotary_dim)
             self._tables = shared
         return self._tables
-
-    tables = rotary_tables
 
 
 def drop_shared_tables() -> None:

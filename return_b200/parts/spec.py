@@ -158,6 +158,40 @@ class MatrixMemorySpec:
 
 
 @dataclass(frozen=True)
+class TimeMixSpec:
+    """Linear attention with a decay per token, head and key row, and a bonus for the token's own pair.  Each of the five
+    projections (r, k, v, output gate, decay) reads its own blend of the token's input with its predecessor's,
+    x + (x' - x) mu.  The decay is exp(-exp(W2 tanh(W1 x_w) + w0)) through a low rank ``decay_rank``.  Per head, with a
+    [key_dim, key_dim] state: o = (S + diag(u) k v^T)^T r, then S <- diag(decay) S + k v^T.  Each head's o is divided by
+    its root mean square, weighted over all heads, gated by silu of the gate projection, and projected out."""
+    hidden_size: int
+    num_heads: int
+    key_dim: int
+    decay_rank: int
+    eps: float
+    kind: str = "time_mix"
+
+
+@dataclass(frozen=True)
+class StateSpaceSpec:
+    """State-space mixer with a scalar decay per token and head.  One projection gives [z | x | B | C | dt]: the gate z
+    and the values x (``num_heads`` heads of ``value_dim``), the input and output maps B and C (``groups`` groups of
+    ``state_dim``; head h uses group h // (num_heads / groups)) and a step per head.  x, B and C pass a causal
+    convolution of ``conv_taps`` taps with a bias, then silu.  dt = softplus(dt + dt_bias); per head
+    S <- exp(-exp(A_log) dt) S + dt B x^T, y = S^T C + D x.  y times silu(z) is normed in ``norm_groups`` equal parts,
+    weighted, and projected out."""
+    hidden_size: int
+    num_heads: int
+    value_dim: int
+    state_dim: int
+    groups: int
+    conv_taps: int
+    norm_groups: int
+    eps: float
+    kind: str = "state_space"
+
+
+@dataclass(frozen=True)
 class MixerSumSpec:
     """Several mixers on the same input; the result is the sum of ``scales[i] * mixers[i](x)``.  ``names`` are the
     children's names in parameter names and cache needs."""
@@ -190,6 +224,16 @@ class SwiGLUSpec:
 
 
 @dataclass(frozen=True)
+class DenseMLPSpec:
+    """down( act(up(x)) ), dense, no gate and no biases.  ``activation``: "relu2" (the square of relu), "gelu_tanh" or
+    "silu"."""
+    hidden_size: int
+    intermediate_size: int
+    activation: str = "relu2"
+    kind: str = "dense_mlp"
+
+
+@dataclass(frozen=True)
 class ClampedGLUSpec:
     """down( g * sigmoid(alpha g) * (u + 1) ) with g = min(gate(x), limit), u = clamp(up(x), -limit, limit); dense, no
     biases."""
@@ -205,8 +249,10 @@ class MoESpec:
     """A mixture of ``num_experts`` feed-forwards of one form (``expert``, a dense feed-forward's specification) of which
     every token uses ``top``.  Router scores are a softmax over all experts (float32); with ``groups`` > 1 the experts
     form that many equal groups of neighbours and only those of the ``keep_groups`` groups with the largest best score
-    can be chosen; the chosen scores divided by their sum (+ ``renorm_tiny``) weigh the experts' outputs.  ``shared``:
-    a feed-forward that runs for every token and is added, or None."""
+    can be chosen; the chosen scores divided by their sum (+ ``renorm_tiny``) weigh the experts' outputs (with
+    ``renorm_tiny`` = 0 that is the softmax over the chosen logits alone).  ``router_bias``: a bias per expert is added to
+    the logits.  ``expert`` is a ``ClampedGLUSpec`` or a ``SwiGLUSpec`` with rows not woven.  ``shared``: a feed-forward
+    that runs for every token and is added, or None."""
     hidden_size: int
     num_experts: int
     top: int
@@ -215,6 +261,7 @@ class MoESpec:
     keep_groups: int = 1
     shared: Any = None
     renorm_tiny: float = 1e-20
+    router_bias: bool = False
     kind: str = "moe"
 
 
@@ -229,6 +276,19 @@ class SandwichBlockSpec:
     feed_forward_norm: Any = None
     feed_forward_post_norm: Any = None
     kind: str = "sandwich"
+
+
+@dataclass(frozen=True)
+class HyperBlockSpec:
+    """A pre-norm layer over ``streams`` residual streams x_1 .. x_S instead of one.  Each sublayer has a read vector
+    a [S], a write vector b [S] and a mixing matrix m [S, S] (indexed [from, to]): it runs on norm(sum_s a[s] x_s),
+    and then x_t <- sum_s m[s, t] x_s + b[t] y for all t at once.  ``feed_forward`` None: the layer has none."""
+    mixer: Any
+    feed_forward: Any
+    mixer_norm: Any
+    feed_forward_norm: Any
+    streams: int
+    kind: str = "hyper"
 
 
 @dataclass(frozen=True)
@@ -259,6 +319,10 @@ class DecoderSpec:
     tie_embeddings: bool
     embedding_norm: Any = None            # a norm applied to the embedded tokens before the first layer
     logit_softcap: Optional[float] = None  # logits <- cap * tanh(logits / cap)
+    embedding_scale: float = 1.0          # the embedded tokens are multiplied by this (the output head is not)
+    streams: Optional[int] = None         # None: one residual stream [T, hidden].  n: a token has n streams
+                                          # ([T, n, hidden]; every block must take them), all start as the embedded
+                                          # token and their sum goes to the final norm
 
     @staticmethod
     def in_order(n_layers: int) -> Tuple[ScheduleEntry, ...]:

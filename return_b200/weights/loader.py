@@ -30,7 +30,8 @@ from .safetensors_io import ModelFiles, write_safetensors
 @dataclass(frozen=True)
 class Source:
     """Checkpoint tensors that make up one parameter: concatenated along dim 0, or, with
-    ``interleave`` = b, woven in blocks of b rows (b rows of the first, b of the second, ...)."""
+    ``interleave`` = b, woven in blocks of b rows (b rows of the first, b of the second, ...).  Tensors with one axis
+    fewer than the parameter are stacked: each becomes one row."""
     names: Tuple[str, ...]
     interleave: int = 0
     # Heads padded with zeros on the way in.  ``pad_rows``: per name, None or (rows of a head in the file, rows of a
@@ -132,6 +133,8 @@ def load_parameters(params: Dict[str, "ParamSpec"], sources: Dict[str, Source],
                 src = sources[pname]
                 for j, n in enumerate(names):
                     t = _pad_heads(files.tensor(n), src.pad_rows[j] if src.pad_rows else None, src.pad_cols)
+                    if 0 < t.dim() < dst.dim():          # vectors stacked into a matrix: each is one row
+                        t = t.unsqueeze(0)
                     k = t.shape[0] if t.dim() else 1
                     view = dst[row:row + k] if t.dim() else dst
                     view.copy_(t)
@@ -161,6 +164,8 @@ def random_tensor(seed: int, name: str, shape, init: str, dtype: torch.dtype, de
         x.mul_(0.1).add_(1.0)
     elif init == "zeros_normal":                   # a weight stored around zero
         x.mul_(0.1)
+    elif init == "uniform01":                      # a blend weight between 0 and 1
+        x = torch.rand(tuple(shape), generator=g, dtype=torch.float32, device=device)
     elif init == "fan_in":                         # deviation inputs^-1/2: outputs as large as inputs
         x.mul_(float(shape[-1]) ** -0.5)
     elif init.startswith("normal:"):
@@ -234,6 +239,10 @@ def random_parameters(params: Dict[str, "ParamSpec"], sources: Dict[str, Source]
                                src.pad_cols)
                 dst[row:row + t.shape[0]].copy_(t)
                 row += t.shape[0]
+                continue
+            if 0 < len(shp) < dst.dim():           # vectors stacked into a matrix: each is one row
+                dst[row].copy_(random_tensor(seed, n, shp, init, dt, device))
+                row += 1
                 continue
             k = shp[0]
             # large matrices are drawn in slabs so that the float32 temporary stays small
