@@ -17,7 +17,7 @@ from typing import Dict, Optional, Tuple
 
 from ..config.model_config import ConfigError
 from ..config.nozizen_config import NozizenConfig
-from ..parts.spec import (AttentionSpec, BlockSpec, DecoderSpec, DenseMLPSpec, HyperBlockSpec, MoESpec, NormSpec,
+from ..parts.spec import (AttentionSpec, DecoderSpec, DenseMLPSpec, HyperBlockSpec, MoESpec, NormSpec,
                           RampedRopeSpec, ScheduleEntry, StateSpaceSpec, SwiGLUSpec, TimeMixSpec)
 from ..weights.loader import Source
 
@@ -72,16 +72,12 @@ def decoder_spec(cfg: NozizenConfig, max_positions: Optional[int] = None) -> Dec
     for layer in cfg.layers:
         ff = _mlp_spec(layer.get("mlp"), W)
         mixer = _mixer_spec(layer["type"], layer["mixer"], W, eps, max_positions)
-        if S is None:
-            if ff is None:
-                raise ConfigError("a layer without a feed-forward needs residual streams (the plain pre-norm block has both sublayers)")
-            blocks.append(BlockSpec(mixer=mixer, feed_forward=ff, mixer_norm=norm, feed_forward_norm=norm))
-        else:
-            blocks.append(HyperBlockSpec(mixer=mixer, feed_forward=ff, mixer_norm=norm, feed_forward_norm=norm if ff else None,
-                                         streams=S))
+        # without the key there is one stream and the plain residual sum: the same block with connections that are all one
+        blocks.append(HyperBlockSpec(mixer=mixer, feed_forward=ff, mixer_norm=norm, feed_forward_norm=norm if ff else None,
+                                     streams=S if S is not None else 1, learned=S is not None))
     schedule = tuple(ScheduleEntry(i) for i in cfg.layer_order())
     return DecoderSpec(vocab_size=cfg.vocab, hidden_size=W, layers=tuple(blocks), schedule=schedule, final_norm=norm,
-                       tie_embeddings=True, embedding_scale=cfg.embedding_scale, streams=S)
+                       tie_embeddings=True, embedding_scale=cfg.embedding_scale, streams=S if S is not None else 1)
 
 
 def weight_sources(cfg: NozizenConfig) -> Dict[str, Source]:
@@ -129,7 +125,9 @@ def weight_sources(cfg: NozizenConfig) -> Dict[str, Source]:
 
 def checkpoint_shapes(cfg: NozizenConfig) -> Dict[str, Tuple[Tuple[int, ...], str]]:
     """Every tensor of a checkpoint: name -> (shape, law of its random values).  Matrices are drawn with a deviation of
-    fan_in^-1/2, norm weights around one, the others so that gates, decays and steps are neither shut nor open."""
+    fan_in^-1/2 (half that for the maps back into the streams, twelve times that for the routers, so that a sublayer adds
+    less than the streams hold and rounding seldom turns a choice), norm weights around one, the streams' connections
+    positive and near the identity, the others so that gates, decays and steps are neither shut nor open."""
     W, V, S = cfg.width, cfg.vocab, cfg.streams
     out: Dict[str, Tuple[Tuple[int, ...], str]] = {"embed": ((V, W), "normal:0.05"), "final.norm": ((W,), "ones_normal")}
     for i, layer in enumerate(cfg.layers):
@@ -139,9 +137,9 @@ def checkpoint_shapes(cfg: NozizenConfig) -> Dict[str, Tuple[Tuple[int, ...], st
         subs = ["hc1"] + (["hc2"] if layer.get("mlp") else [])
         if S is not None:
             for hc in subs:
-                out[f"{p}{hc}.in"] = ((S,), "ones_normal")
-                out[f"{p}{hc}.out"] = ((S,), "ones_normal")
-                out[f"{p}{hc}.mix"] = ((S, S), "normal:0.4")
+                out[f"{p}{hc}.in"] = ((S,), "half_to_one")
+                out[f"{p}{hc}.out"] = ((S,), "half_to_one")
+                out[f"{p}{hc}.mix"] = ((S, S), "eye_normal")
         if kind == "wkv":
             if "decay_rank" not in m:
                 raise ConfigError("a wkv mixer needs decay_rank to size its tensors")
@@ -155,7 +153,7 @@ def checkpoint_shapes(cfg: NozizenConfig) -> Dict[str, Tuple[Tuple[int, ...], st
             out[x + "w0"] = ((H * D,), "normal:0.7")
             out[x + "u"] = ((H, D), "normal:0.5")
             out[x + "norm"] = ((H * D,), "ones_normal")
-            out[x + "o"] = ((W, H * D), "fan_in")
+            out[x + "o"] = ((W, H * D), "fan_in:0.5")
         elif kind == "mamba2":
             H, P, N, G, K = int(m["heads"]), int(m["vdim"]), int(m["state"]), int(m["groups"]), int(m["conv"])
             C = H * P + 2 * G * N
@@ -166,13 +164,13 @@ def checkpoint_shapes(cfg: NozizenConfig) -> Dict[str, Tuple[Tuple[int, ...], st
             out[x + "A_log"] = ((H,), "normal:0.5")
             out[x + "D"] = ((H,), "ones_normal")
             out[x + "norm"] = ((H * P,), "ones_normal")
-            out[x + "o"] = ((W, H * P), "fan_in")
+            out[x + "o"] = ((W, H * P), "fan_in:0.5")
         else:
             H, G, D, Vd = int(m["heads"]), int(m["kv_heads"]), int(m["dim"]), int(m["vdim"])
             out[x + "q"] = ((H * D, W), "fan_in")
             out[x + "k"] = ((G * D, W), "fan_in")
             out[x + "v"] = ((G * Vd, W), "fan_in")
-            out[x + "o"] = ((W, H * Vd), "fan_in")
+            out[x + "o"] = ((W, H * Vd), "fan_in:0.5")
         mlp = layer.get("mlp")
         if mlp:
             y = p + "mlp."
@@ -180,15 +178,15 @@ def checkpoint_shapes(cfg: NozizenConfig) -> Dict[str, Tuple[Tuple[int, ...], st
             if mlp["kind"] == "dense":
                 ff = int(mlp["ff"])
                 out[y + "up"] = ((ff, W), "fan_in")
-                out[y + "down"] = ((W, ff), "fan_in")
+                out[y + "down"] = ((W, ff), "fan_in:0.5")
             else:
                 E, F = int(mlp["router"]["experts"]), int(mlp["expert"]["ff"])
-                out[y + "router"] = ((E, W), "fan_in")
-                out[y + "router.b"] = ((E,), "normal:0.5")
+                out[y + "router"] = ((E, W), "fan_in:12")         # choices that rounding seldom turns
+                out[y + "router.b"] = ((E,), "normal:4")
                 for j in range(E):
                     out[f"{y}e{j}.gate"] = ((F, W), "fan_in")
                     out[f"{y}e{j}.up"] = ((F, W), "fan_in")
-                    out[f"{y}e{j}.down"] = ((W, F), "fan_in")
+                    out[f"{y}e{j}.down"] = ((W, F), "fan_in:0.5")
     return out
 
 

@@ -319,10 +319,10 @@ class HyperBlock(Block):
     def params(self):
         S = self.spec.streams
         p = {f"{child}.{name}": ps for child, part in self._children.items() for name, ps in part.params().items()}
-        for sub in self._sublayers:
-            p[f"{sub}_read"] = ParamSpec((S,), role="vector", init="ones_normal")
-            p[f"{sub}_write"] = ParamSpec((S,), role="vector", init="ones_normal")
-            p[f"{sub}_mix"] = ParamSpec((S, S), role="vector", init="normal:0.4")
+        for sub in self._sublayers if self.spec.learned else ():
+            p[f"{sub}_read"] = ParamSpec((S,), role="vector", init="half_to_one")
+            p[f"{sub}_write"] = ParamSpec((S,), role="vector", init="half_to_one")
+            p[f"{sub}_mix"] = ParamSpec((S, S), role="vector", init="eye_normal")
         return p
 
     def bind(self, tensors):
@@ -330,8 +330,14 @@ class HyperBlock(Block):
             prefix = child + "."
             part.bind({k[len(prefix):]: v for k, v in tensors.items() if k.startswith(prefix)})
         # the streams' arithmetic is float32 whatever the checkpoint stores
-        self.hc = {sub: tuple(tensors[f"{sub}_{n}"].float().contiguous() for n in ("read", "write", "mix"))
-                   for sub in self._sublayers}
+        if self.spec.learned:
+            self.hc = {sub: tuple(tensors[f"{sub}_{n}"].float().contiguous() for n in ("read", "write", "mix"))
+                       for sub in self._sublayers}
+        else:
+            S, dev = self.spec.streams, self.env.device
+            ones = (torch.ones(S, dtype=torch.float32, device=dev), torch.ones(S, dtype=torch.float32, device=dev),
+                    torch.ones((S, S), dtype=torch.float32, device=dev))
+            self.hc = {sub: ones for sub in self._sublayers}
 
     def cache_need(self):
         return self.mixer.cache_need()

@@ -282,12 +282,15 @@ class SandwichBlockSpec:
 class HyperBlockSpec:
     """A pre-norm layer over ``streams`` residual streams x_1 .. x_S instead of one.  Each sublayer has a read vector
     a [S], a write vector b [S] and a mixing matrix m [S, S] (indexed [from, to]): it runs on norm(sum_s a[s] x_s),
-    and then x_t <- sum_s m[s, t] x_s + b[t] y for all t at once.  ``feed_forward`` None: the layer has none."""
+    and then x_t <- sum_s m[s, t] x_s + b[t] y for all t at once.  ``feed_forward`` None: the layer has none.
+    ``learned`` False: a, b and m are not parameters but all one, which with one stream is the plain residual sum
+    x <- x + y."""
     mixer: Any
     feed_forward: Any
     mixer_norm: Any
     feed_forward_norm: Any
     streams: int
+    learned: bool = True
     kind: str = "hyper"
 
 

@@ -166,8 +166,14 @@ def random_tensor(seed: int, name: str, shape, init: str, dtype: torch.dtype, de
         x.mul_(0.1)
     elif init == "uniform01":                      # a blend weight between 0 and 1
         x = torch.rand(tuple(shape), generator=g, dtype=torch.float32, device=device)
+    elif init == "half_to_one":                    # a positive weight: sums of such never cancel
+        x = 0.5 + 0.5 * torch.rand(tuple(shape), generator=g, dtype=torch.float32, device=device)
+    elif init == "eye_normal":                     # a square matrix near the identity
+        x.mul_(0.1).add_(torch.eye(shape[0], shape[1], dtype=torch.float32, device=device))
     elif init == "fan_in":                         # deviation inputs^-1/2: outputs as large as inputs
         x.mul_(float(shape[-1]) ** -0.5)
+    elif init.startswith("fan_in:"):               # the same times a gain
+        x.mul_(float(init.split(":", 1)[1]) * float(shape[-1]) ** -0.5)
     elif init.startswith("normal:"):
         x.mul_(float(init.split(":", 1)[1]))
     else:

@@ -235,7 +235,7 @@ def forward(c, w, ids, keep_layers=False):
     """(logits [T, vocab], the sum of the streams after every layer run or None)."""
     eps = c["norm"]["eps"]
     dtype = w["embed"].dtype
-    x = w["embed"][torch.tensor(ids)] * c["embedding"]["scale"]
+    x = w["embed"][torch.tensor(ids)] * (c.get("embedding") or {}).get("scale", 1.0)
     hyper = c.get("streams") is not None          # without the key: one stream and plain residual sums
     S = int(c["streams"]) if hyper else 1
     xs = x[None].repeat(S, 1, 1)
