@@ -429,7 +429,8 @@ def run_workload(name: str, layers: int = 0, new: int = 0) -> Dict[str, object]:
 
 def kernel_scan(mode=0, batch=1, tokens=2048, heads=16, kv_heads=0, dim=128, vdim=128, iters=10, warmup=3) -> Dict[str, object]:
     """The recurrence kernel of the mixers with a matrix state alone: ``batch`` segments of ``tokens`` tokens each
-    (tokens = 1: a decode step).  mode 0: fixed decay, 1: matrix memory, 2: delta rule.  Reports the time of a launch,
+    (tokens = 1: a decode step).  mode 0: fixed decay, 1: matrix memory, 2: delta rule, 3: row decays with a bonus, 4: state
+    space.  Reports the time of a launch,
     the float32 operations per second, and the bandwidth on the states (each read and written once)."""
     from types import SimpleNamespace
     from .ext import ops
@@ -451,11 +452,19 @@ def kernel_scan(mode=0, batch=1, tokens=2048, heads=16, kv_heads=0, dim=128, vdi
         ga, gb = torch.linspace(0.97, 0.999, heads, device=dev), None
     elif mode == ops.SCAN_MEMORY:
         ga, gb = rnd(T, 2 * heads), torch.zeros(2 * heads, device=dev)
+    elif mode == ops.SCAN_SSM:
+        ga, gb = torch.sigmoid(rnd(T, heads) + 3.0).contiguous(), torch.sigmoid(rnd(T, heads)).contiguous()
     else:
         ga, gb = torch.sigmoid(rnd(T, heads * dim) + 3.0).contiguous(), torch.sigmoid(rnd(T, heads)).contiguous()
+    extra = None
+    if mode == ops.SCAN_BONUS:
+        gb, extra = None, rnd(heads * dim)
+    elif mode == ops.SCAN_SSM:
+        extra = rnd(heads)
     out = torch.empty((T, heads * vdim), device=dev)
     fns = [(lambda st=st: ops.linear_scan(mode, q, k, v, ga, gb, st, (0, n_off, m_off), b, out, heads, G, dim, vdim,
-                                          q_scale=dim ** -0.5, cap=15.0)) for st in states]
+                                          q_scale=dim ** -0.5 if mode < ops.SCAN_BONUS else 1.0, cap=15.0, extra=extra))
+           for st in states]
     ms = _time_kernels(fns, iters, warmup)
     flops = T * heads * dim * vdim * (6.0 if mode == ops.SCAN_DELTA else 4.0)
     return {"kernel": "linear_scan", "mode": mode, "batch": batch, "tokens": tokens, "heads": heads, "dim": dim, "vdim": vdim,
@@ -685,3 +694,91 @@ def compare_gonozen(size: str, tokens: int, batch: int, steps: int, warmup: int,
         del r["prefill_kernels"], r["decode_kernels"]
     return {"size": size, "width": W, "ff": ff, "heads": H, "layers": L, "tokens": tokens, "batch": batch,
             "experts": mlp["router"], "expert_ff": F, "gonozen": new, "qwen3": old, "kernels": kernels}
+
+
+def nozizen_raw_config(width: int, ff: int, heads: int, kv_heads: int, layers: int, vocab: int, window: int = 1024,
+                       streams: int = 4) -> dict:
+    """A Nozizen configuration whose mixers carry as many heads of 128 as the attention of a Qwen3 model of this width:
+    of every four layers the first is a time mix (states of 128 x 128), the next two state-space mixers (a state of 128
+    rows for a head's 128 values, ``kv_heads`` groups, four taps), the fourth a windowed attention (rotation over half a
+    head, stretched); the first and third feed-forwards are dense, the others 32 experts of a quarter of the dense size
+    each, four of them a token, so that a token's experts do the dense feed-forward's work."""
+    dense = {"kind": "dense", "ff": ff}
+    experts = {"kind": "moe", "router": {"experts": 32, "top": 4}, "expert": {"ff": ff // 4}}
+    time_mix = {"type": "wkv", "mixer": {"heads": heads, "dim": 128, "decay_rank": 64}}
+    space = {"type": "mamba2", "mixer": {"heads": heads, "vdim": 128, "state": 128, "groups": kv_heads, "conv": 4,
+                                         "norm_groups": kv_heads}}
+    attention = {"type": "attention",
+                 "mixer": {"heads": heads, "kv_heads": kv_heads, "dim": 128, "vdim": 128, "scale": 128 ** -0.5,
+                           "mask": {"size": window},
+                           "rot": {"base": 1e4, "dims": 64, "scaling": {"factor": 8.0, "original": 2048, "fast": 32.0, "slow": 1.0}}}}
+    pattern = [(time_mix, dense), (space, experts), (space, dense), (attention, experts)]
+    return {"architecture": "Nozizen", "vocab": vocab, "width": width, "norm": {"eps": 1e-5},
+            "embedding": {"scale": float(width) ** 0.5}, "streams": streams,
+            "layers": [dict(pattern[i % 4][0], mlp=pattern[i % 4][1]) for i in range(layers)]}
+
+
+def compare_nozizen(size: str, tokens: int, batch: int, steps: int, warmup: int, hbm_gbs: float, bf16_tflops: float):
+    """The Nozizen design beside the Pisatar decoder (the nearest the engine has: state mixers on the same scan kernel,
+    a softmax attention, dense feed-forwards) at equal width, feed-forward, layer count and heads: throughput of both,
+    and how far the kernels of each mechanism are from their rooflines beside the like kernels of the other model.
+    Rooflines: the scan over decoded tokens against the copy bandwidth (every state read and written once); the scan
+    over a prompt against the tensor peak (4 T heads dim vdim operations, as for the Pisatar row, although the scan
+    runs in float32 on the CUDA cores); attention over decoded tokens against the copy bandwidth (the keys and values
+    the window shows read once); attention over a prompt against the tensor peak (the causal half, or the window's
+    band); the kernels that read and write the residual streams against the copy bandwidth (each stream read and
+    written once a sublayer, beside Pisatar's add-and-norm kernel over its one stream); the experts' products of a
+    prompt against the tensor peak and of decoded tokens against the copy bandwidth (each reached expert read once)."""
+    from .config.nozizen_config import NozizenConfig
+    from .config.pisatar_config import PisatarConfig
+    sz = DESIGN_SIZES[size]
+    W, ff, H, G, L, V = sz["width"], sz["ff"], sz["heads"], sz["kv_heads"], sz["layers"], sz["vocab"]
+    raw = nozizen_raw_config(W, ff, H, G, L, V)
+    new = measure_design(NozizenConfig(raw), tokens, batch, steps, warmup)
+    old = measure_design(PisatarConfig(pisatar_raw_config(W, ff, H, G, L, V)), tokens, batch, steps, warmup)
+    D, S = 128, raw["streams"]
+    kinds = [layer["type"] for layer in raw["layers"]]
+    n_state, n_att = kinds.count("wkv") + kinds.count("mamba2"), kinds.count("attention")
+    n_moe = sum(1 for layer in raw["layers"] if layer["mlp"]["kind"] == "moe")
+    window = raw["layers"][3]["mixer"]["mask"]["size"] if L > 3 else tokens
+    seen = min(tokens, window)
+    frac = lambda work, ms, peak: round(work / (ms * 1e-3) / peak, 4) if ms > 0 else None
+    state_bytes_new = 4.0 * D * D * H * n_state
+    scan_flops_new = 4.0 * tokens * D * D * H * n_state
+    o_ret, o_delta, o_both = (L + 3) // 4 + (L + 2) // 4, (L + 1) // 4, L // 4
+    state_bytes_old = 4.0 * D * (o_ret * H * 128 + o_delta * H * 128 + o_both * (H // 2) * 256)
+    scan_flops_old = tokens * D * (4.0 * o_ret * H * 128 + 6.0 * o_delta * H * 128 + 4.0 * o_both * (H // 2) * 256)
+    band = tokens * tokens / 2 if window >= tokens else tokens * window - window * window / 2
+    F, top, E = ff // 4, 4, 32
+    distinct = E * (1.0 - (1.0 - 1.0 / E) ** (batch * top))
+    k_new, k_old, d_new, d_old = new["prefill_kernels"], old["prefill_kernels"], new["decode_kernels"], old["decode_kernels"]
+    att_pf, att_dec = ("attn_prefill", "attention_tc5", "merge_key_splits", "tc5_merge"), ("attn_decode", "attn_combine")
+    hyper = ("hyper_read_norm", "hyper_write")
+    moe_pf, moe_dec = ("moe_grouped_gemm", "moe_tc5"), ("moe_pair_linear", "moe_grouped_gemm")
+    small = ("token_shift_mix", "ssm_prep", "conv_state_update", "gated_part_norm", "head_norm_gate", "activation_kernel",
+             "clamped_glu", "moe_combine", "moe_route", "moe_sort", "moe_gather")
+    hbm, peak = hbm_gbs * 1e9, bf16_tflops * 1e12
+    row = lambda times, names, work, roof, key: {"ms": round(_kernel_ms(times, *names), 4), key: frac(work, _kernel_ms(times, *names), roof)}
+    kernels = {
+        "decode_scan_nozizen": row(d_new, ("linear_scan",), 2.0 * state_bytes_new * batch, hbm, "of_hbm"),
+        "decode_scan_pisatar": row(d_old, ("linear_scan",), 2.0 * state_bytes_old * batch, hbm, "of_hbm"),
+        "prefill_scan_nozizen": row(k_new, ("linear_scan",), scan_flops_new, peak, "of_bf16_peak"),
+        "prefill_scan_pisatar": row(k_old, ("linear_scan",), scan_flops_old, peak, "of_bf16_peak"),
+        "decode_attention_nozizen": row(d_new, att_dec, 2.0 * 2 * G * D * seen * batch * n_att, hbm, "of_hbm"),
+        "decode_attention_pisatar": row(d_old, att_dec, 2.0 * 2 * G * D * tokens * batch * o_both, hbm, "of_hbm"),
+        "prefill_attention_nozizen": row(k_new, att_pf, 4.0 * band * H * D * n_att, peak, "of_bf16_peak"),
+        "prefill_attention_pisatar": row(k_old, att_pf, 4.0 * tokens * tokens / 2 * H * D * o_both, peak, "of_bf16_peak"),
+        # a sublayer's read and write: S streams of float32 read twice and written once, the normed rows written
+        "prefill_streams_nozizen": row(k_new, hyper, (2 * L - 0) * tokens * W * (3.0 * S * 4 + 2 * 2), hbm, "of_hbm"),
+        "prefill_add_norm_pisatar": row(k_old, ("add_dual_norm",), L * tokens * W * (2.0 * 4 + 2 * 2 + 2 * 2), hbm, "of_hbm"),
+        "prefill_experts_nozizen": row(k_new, moe_pf, n_moe * 2.0 * tokens * top * 3 * F * W, peak, "of_bf16_peak"),
+        "decode_experts_nozizen": row(d_new, moe_dec, n_moe * 2.0 * distinct * 3 * F * W, hbm, "of_hbm"),
+        "prefill_small_kernels_nozizen": {"ms": round(_kernel_ms(k_new, *small), 4),
+                                          "note": "blends, convolution, gates and norms around the scans, the activation, the experts' helpers"},
+        "decode_streams_nozizen": {"ms": round(_kernel_ms(d_new, *hyper), 4)},
+        "decode_small_kernels_nozizen": {"ms": round(_kernel_ms(d_new, *small), 4)},
+    }
+    for r in (new, old):
+        del r["prefill_kernels"], r["decode_kernels"]
+    return {"size": size, "width": W, "ff": ff, "heads": H, "kv_heads": G, "layers": L, "tokens": tokens, "batch": batch,
+            "streams": S, "window": window, "nozizen": new, "pisatar": old, "kernels": kernels}

@@ -383,6 +383,65 @@ RB_EXPORT int rb_scan_pieces_combine(float* pieces, long long piece_stride, floa
                          decay, cu_piece, seg_first, seg_slot, per_head, total);
 }
 
+// The same for decays that differ from token to token: per head (the state-space scan) or per head and key row (the
+// scan with a bonus).  A piece's transition is then the product of its tokens' decays, which the first kernel leaves as
+// a sum of logarithms per piece (a decay of zero gives minus infinity and a factor of zero); the second is the walk above with that factor.  An element e of a head's matrix
+// belongs to key row (e / (8 V)) * 8 + e % 8 of the layout [row / 8][column][row % 8].
+__global__ void piece_decay_sums_kernel(const float* __restrict__ decay, int n, const int* __restrict__ cu_piece,
+                                        float* __restrict__ sums) {
+    // 64 columns by 8 runs of tokens (token t of the piece goes to run t % 8); the runs are added in their order
+    __shared__ float part[8][64];
+    pdl_wait();
+    const int p = blockIdx.y, i = blockIdx.x * 64 + threadIdx.x;
+    float acc = 0.f;
+    if (i < n)
+        for (int t = cu_piece[p] + threadIdx.y; t < cu_piece[p + 1]; t += 8) acc += logf(decay[(size_t)t * n + i]);
+    part[threadIdx.y][threadIdx.x] = acc;
+    __syncthreads();
+    if (threadIdx.y == 0 && i < n) {
+#pragma unroll
+        for (int y = 1; y < 8; ++y) acc += part[y][threadIdx.x];
+        sums[(size_t)p * n + i] = acc;
+    }
+}
+
+__global__ void scan_pieces_combine_sums_kernel(float* __restrict__ pieces, long long piece_stride, float* __restrict__ state,
+                                                long long state_stride, int s_off, const float* __restrict__ sums, int n,
+                                                int by_row, int D, int V, const int* __restrict__ seg_first,
+                                                const int* __restrict__ seg_slot, int per_head, int total) {
+    pdl_wait();
+    const int seg = blockIdx.y;
+    const int e = blockIdx.x * blockDim.x + threadIdx.x;
+    if (e >= total) return;
+    const int h = e / per_head, rem = e - h * per_head;
+    const int row = (rem / (8 * V)) * 8 + (rem & 7);
+    float* home = state + (long long)seg_slot[seg] * state_stride + s_off + e;
+    if (by_row && row >= D) return;                     // a padding row: it holds zero and stays zero
+    const int col = by_row ? h * D + row : h;
+    float carry = *home;
+    for (int p = seg_first[seg]; p < seg_first[seg + 1]; ++p) {
+        float* at = pieces + (long long)p * piece_stride + e;
+        const float left = *at;
+        *at = carry;
+        carry = fmaf(expf(sums[(size_t)p * n + col]), carry, left);
+    }
+    *home = carry;
+}
+
+// decay: float32 [T, n] (n = heads, or heads * D with by_row); sums: float32 scratch [pieces, n]
+RB_EXPORT int rb_scan_pieces_combine_sums(float* pieces, long long piece_stride, float* state, long long state_stride, int s_off,
+                                          const float* decay, float* sums, int n, int by_row, int D, int V,
+                                          const int* cu_piece, const int* seg_first, const int* seg_slot, int per_head,
+                                          int total, int n_pieces, int segments, cudaStream_t st) {
+    if (segments <= 0 || total <= 0 || n_pieces <= 0) return 0;
+    if (per_head % (8 * V) || n <= 0) return (int)cudaErrorInvalidValue;
+    int rc = rb_launch_pdl(piece_decay_sums_kernel, dim3((n + 63) / 64, n_pieces), dim3(64, 8), 0, st, decay, n, cu_piece, sums);
+    if (rc) return rc;
+    dim3 grid((total + 255) / 256, segments);
+    return rb_launch_pdl(scan_pieces_combine_sums_kernel, grid, dim3(256), 0, st, pieces, piece_stride, state, state_stride,
+                         s_off, (const float*)sums, n, by_row, D, V, seg_first, seg_slot, per_head, total);
+}
+
 // The same for the matrix memory.  A piece scanned from nothing (S = 0, n = 0, m = -infinity) leaves S', n', its own
 // running maximum m' and F, the sum of its log forget gates; behind a state (S0, n0, m0) the piece ends in
 //     m = max(F + m0, m'),   S = e^(F + m0 - m) S0 + e^(m' - m) S',   n likewise.

@@ -876,6 +876,8 @@ def recurrent_lib() -> ctypes.CDLL:
         lib.rb_rotary_to_f32.argtypes = [P, I, I, I, P, P, I, P, P, P, I, I, I, I, F, F, P]
         lib.rb_scan_pieces_combine.argtypes = [P, L, P, L, I, P, P, P, P, I, I, I, P]
         lib.rb_scan_pieces_combine.restype = c_int
+        lib.rb_scan_pieces_combine_sums.argtypes = [P, L, P, L, I, P, P, I, I, I, I, P, P, P, I, I, I, I, P]
+        lib.rb_scan_pieces_combine_sums.restype = c_int
         lib.rb_memory_pieces_combine.argtypes = [P, L, P, L, I, I, I, I, P, P, I, I, I, I, P]
         lib.rb_memory_pieces_combine.restype = c_int
         lib.rb_rotary_inplace.argtypes = [P, I, P, P, I, P, I, I, I, I, P]
@@ -941,6 +943,22 @@ def scan_pieces_combine(pieces, state, s_off: int, decay, cu_piece, seg_first, s
     _check(recurrent_lib().rb_scan_pieces_combine(_ptr(pieces), pieces.stride(0), _ptr(state), state.stride(0), s_off,
                                                   _ptr(decay), _ptr(cu_piece), _ptr(seg_first), _ptr(seg_slot), per_head,
                                                   total, segments, _stream()), "scan_pieces_combine")
+
+
+def scan_pieces_combine_sums(pieces, state, s_off: int, decay, sums, by_row: bool, dim: int, vdim: int, cu_piece, seg_first,
+                             seg_slot, per_head: int, total: int, segments: int) -> None:
+    """``scan_pieces_combine`` for decays that differ from token to token: ``decay`` float32 [T, n] holds one per head
+    (n = heads) or, with ``by_row``, one per head and key row (n = heads * dim); a piece's factor is the product of its
+    tokens' decays, left as sums of logarithms in ``sums`` (float32 scratch [pieces, n])."""
+    n_pieces = cu_piece.numel() - 1
+    assert pieces.dtype == state.dtype == decay.dtype == sums.dtype == torch.float32
+    assert pieces.is_contiguous() and state.is_contiguous() and decay.is_contiguous() and sums.is_contiguous()
+    assert decay.dim() == 2 and sums.shape == (n_pieces, decay.shape[1])
+    assert cu_piece.dtype == seg_first.dtype == seg_slot.dtype == torch.int32
+    _check(recurrent_lib().rb_scan_pieces_combine_sums(
+        _ptr(pieces), pieces.stride(0), _ptr(state), state.stride(0), s_off, _ptr(decay), _ptr(sums), decay.shape[1],
+        1 if by_row else 0, dim, vdim, _ptr(cu_piece), _ptr(seg_first), _ptr(seg_slot), per_head, total, n_pieces, segments,
+        _stream()), "scan_pieces_combine_sums", 2)
 
 
 def memory_pieces_combine(pieces, state, offsets, forgot_offset: int, seg_first, seg_slot, per_head_s: int, per_head_n: int,

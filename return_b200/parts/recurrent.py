@@ -76,6 +76,25 @@ class _StateMixer(Mixer):
         return plan
 
 
+    def _scan(self, mode, q, k, v, decay, step, ctx, out, groups, extra, by_row, pieces):
+        """The scan of a mixer whose decays differ from token to token (per head, or per head and key row with
+        ``by_row``).  With ``pieces`` the long segments are scanned in pieces side by side: every piece from zero, the
+        states handed on in order (a piece's transition is the product of its tokens' decays), every piece again."""
+        b = ctx.batch
+        if pieces is None:
+            ops.linear_scan(mode, q, k, v, decay, step, ctx.state, (0, 0, 0), b, out, self.H, groups, self.D, self.V, extra=extra)
+            return
+        virtual, seg_first, n_pieces = pieces
+        dev = out.device
+        held = ctx.buffer(self.spec.kind + ".pieces", (n_pieces, self.s_floats), torch.float32, dev)
+        sums = ctx.buffer(self.spec.kind + ".piece_decays", (n_pieces, decay.shape[1]), torch.float32, dev)
+        held.zero_()
+        for again in (False, True):
+            ops.linear_scan(mode, q, k, v, decay, step, held, (0, 0, 0), virtual, out, self.H, groups, self.D, self.V, extra=extra)
+            if not again:
+                ops.scan_pieces_combine_sums(held, ctx.state, 0, decay, sums, by_row, self.D, self.V, virtual.cu_q, seg_first,
+                                             b.seg_slot, _pad8(self.D) * self.V, self.s_floats, b.num_segments)
+
     def _project_out(self, mixed, ctx):
         y = ctx.buffer(self.spec.kind + ".y", (mixed.shape[0], self.spec.hidden_size), torch.float32, mixed.device)
         ops.linear(mixed, self.p_o, y)
@@ -307,8 +326,8 @@ class TimeMix(_StateMixer):
         ops.linear(low, self.p_decay_up, decay)
         ops.activation(decay, decay, "neg_exp_exp", bias=self.p_decay_bias)
         o = ctx.buffer("time_mix.o", (T, HD), torch.float32, dev)
-        ops.linear_scan(ops.SCAN_BONUS, proj[0], proj[1], proj[2], decay, None, ctx.state, (0, 0, 0), b, o,
-                        self.H, self.H, self.D, self.V, extra=self._bonus32)
+        self._scan(ops.SCAN_BONUS, proj[0], proj[1], proj[2], decay, None, ctx, o, self.H, self._bonus32, True,
+                   self._pieces(b) if dt != torch.float32 else None)
         mixed = ctx.buffer("time_mix.mixed", (T, HD), dt, dev)
         ops.head_norm_gate(o, proj[3], self.p_norm, 2, 0, s.eps, mixed, self.H, self.V)
         return self._project_out(mixed, ctx)
@@ -369,8 +388,8 @@ class StateSpace(_StateMixer):
                      self.p_dt_bias, self.p_A_log, step, decay)
         ops.conv_state_update(proj[:, inner:], s.conv_taps, ctx.state, self.conv_off, b, C)   # after every token read the old one
         y = ctx.buffer("state_space.y", (T, inner), torch.float32, dev)
-        ops.linear_scan(ops.SCAN_SSM, conv[:, inner + GN:], conv[:, inner:inner + GN], conv[:, :inner], decay, step, ctx.state,
-                        (0, 0, 0), b, y, self.H, s.groups, self.D, self.V, extra=self._skip32)
+        self._scan(ops.SCAN_SSM, conv[:, inner + GN:], conv[:, inner:inner + GN], conv[:, :inner], decay, step, ctx, y,
+                   s.groups, self._skip32, False, self._pieces(b) if x.dtype != torch.float32 else None)
         mixed = ctx.buffer("state_space.mixed", (T, inner), x.dtype, dev)
         ops.gated_part_norm(y, proj[:, :inner], self.p_norm, s.norm_groups, s.eps, mixed)
         return self._project_out(mixed, ctx)

@@ -652,6 +652,42 @@ def test_long_decoding(tmp_path_factory, dtype, graph):
         assert_close(got[rid], plain_rows(entry, ids)[2:], dtype, rid)
 
 
+def test_a_long_prompt_scanned_in_pieces_side_by_side(tmp_path_factory, monkeypatch):
+    """On the bfloat16 path a time mix and a state-space mixer cut a portion of 1,024 tokens or more into pieces that
+    are scanned at the same time, hand the states from piece to piece (a piece's transition is the product of its
+    tokens' decays, per key row or per head) and scan again.  The outputs of every piece, the state that the tokens
+    decoded afterwards start from, and a short request in the same step must all be right; the decays are slow, so a
+    state handed on wrongly would show to the end.  The float32 path never cuts."""
+    from return_b200.ext import ops
+    raw = config([wkv_layer(heads=2, dim=24, rank=4, mlp=None), ssm_layer(heads=3, vdim=16, state=24, groups=1, conv=3, norm_groups=1, mlp=None),
+                  wkv_layer(heads=1, dim=40, rank=2, mlp=dense(32)), ssm_layer(heads=2, vdim=40, state=8, groups=2, conv=2, norm_groups=2, mlp=None)],
+                 width=32, streams=2)
+    entry = model(tmp_path_factory, "pieces", raw, patch=_slow_decays)
+    reqs = requests_for(entry, (1300, 40), seed=80)
+    long_ids, short_ids = reqs["r0"], reqs["r1"]
+    steps = [{"step": 0, "entries": [{"id": "r1", "tokens": short_ids[:30], "want": list(range(30))}], "end": []},
+             {"step": 1, "entries": [{"id": "r0", "tokens": long_ids[:100], "want": list(range(100))},
+                                      {"id": "r1", "tokens": short_ids[30:31], "want": [0]}], "end": []},
+             {"step": 2, "entries": [{"id": "r1", "tokens": short_ids[31:32], "want": [0]},
+                                      {"id": "r0", "tokens": long_ids[100:1290], "want": list(range(1190))}], "end": []}]
+    for k in range(8):
+        steps.append({"step": 3 + k, "entries": [{"id": "r0", "tokens": [long_ids[1290 + k]], "want": [0]},
+                                                  {"id": "r1", "tokens": [short_ids[32 + k]], "want": [0]}],
+                      "end": ["r0", "r1"] if k == 7 else []})
+    calls, combine = [], ops.scan_pieces_combine_sums
+    monkeypatch.setattr(ops, "scan_pieces_combine_sums", lambda *a, **k: (calls.append(a[5]), combine(*a, **k))[1])
+    got = run_trace(entry[0], "bfloat16", steps)
+    assert calls == [True, False, True, False]                       # once a layer, in the step that holds the long portion
+    assert_close(got["r0"][:1298], plain_rows(entry, long_ids)[:1298], "bfloat16", "long")
+    assert_close(got["r1"], plain_rows(entry, short_ids), "bfloat16", "short")
+    one = run_trace(entry[0], "bfloat16", tail_decoded({"r0": long_ids[:1000]}, tail=8))
+    assert len(calls) == 4                                           # a portion of 992 tokens is walked in one go
+    assert_close(got["r0"][:1000], one["r0"], "bfloat16", "pieces against one walk")
+    exact = run_trace(entry[0], "float32", steps)
+    assert len(calls) == 4
+    assert_close(exact["r0"][:1298], plain_rows(entry, long_ids)[:1298], "float32", "long")
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_other_sizes(tmp_path_factory, dtype):
     entry = model(tmp_path_factory, "other", other_sizes_config(), seed=11)
