@@ -768,8 +768,9 @@ def compare_nozizen(size: str, tokens: int, batch: int, steps: int, warmup: int,
         "decode_attention_pisatar": row(d_old, att_dec, 2.0 * 2 * G * D * tokens * batch * o_both, hbm, "of_hbm"),
         "prefill_attention_nozizen": row(k_new, att_pf, 4.0 * band * H * D * n_att, peak, "of_bf16_peak"),
         "prefill_attention_pisatar": row(k_old, att_pf, 4.0 * tokens * tokens / 2 * H * D * o_both, peak, "of_bf16_peak"),
-        # a sublayer's read and write: S streams of float32 read twice and written once, the normed rows written
-        "prefill_streams_nozizen": row(k_new, hyper, (2 * L - 0) * tokens * W * (3.0 * S * 4 + 2 * 2), hbm, "of_hbm"),
+        # a sublayer's write does the next read as well: S streams of float32 read and written once, the sublayer's
+        # output read and the next normed rows written (the first layer's own read comes to one sublayer in 2 L)
+        "prefill_streams_nozizen": row(k_new, hyper, 2 * L * tokens * W * (2.0 * S * 4 + 2 * 2), hbm, "of_hbm"),
         "prefill_add_norm_pisatar": row(k_old, ("add_dual_norm",), L * tokens * W * (2.0 * 4 + 2 * 2 + 2 * 2), hbm, "of_hbm"),
         "prefill_experts_nozizen": row(k_new, moe_pf, n_moe * 2.0 * tokens * top * 3 * F * W, peak, "of_bf16_peak"),
         "decode_experts_nozizen": row(d_new, moe_dec, n_moe * 2.0 * distinct * 3 * F * W, hbm, "of_hbm"),
