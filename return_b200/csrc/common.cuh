@@ -63,6 +63,22 @@ __device__ __forceinline__ float load_as_f32(const void* p, int dtype, size_t i)
     return dtype == RB_F32 ? ((const float*)p)[i] : __bfloat162float(((const bf16*)p)[i]);
 }
 
+// One-argument activations, float32 arithmetic.  0: relu(x)^2    1: tanh(x)    2: 0.5 x (1 + tanh(sqrt(2/pi) (x + 0.044715 x^3)))
+// 3: x sigmoid(x)    4: exp(-exp(x + b[c])): a decay in (0, 1) from its doubly logarithmic form, with a bias per column.
+#define ACT_RELU2 0
+#define ACT_TANH 1
+#define ACT_GELU_TANH 2
+#define ACT_SILU 3
+#define ACT_NEG_EXP_EXP 4
+
+__device__ __forceinline__ float rb_activate(int op, float v, const void* bias, int bias_dtype, size_t c) {
+    if (op == ACT_RELU2) { const float p = fmaxf(v, 0.f); return p * p; }
+    if (op == ACT_TANH) return tanhf(v);
+    if (op == ACT_GELU_TANH) return 0.5f * v * (1.0f + tanhf(0.7978845608028654f * (v + 0.044715f * v * v * v)));
+    if (op == ACT_SILU) return v / (1.0f + expf(-v));
+    return expf(-expf(v + (bias ? load_as_f32(bias, bias_dtype, c) : 0.f)));
+}
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);

@@ -411,14 +411,7 @@ RB_EXPORT int rb_softcap(float* x, float cap, long long total, cudaStream_t st) 
 
 // ---------------------------------------------------------------- one-argument activations over rows
 // out[r, c] = f(x[r, c]) for rows of `cols` elements with their own strides; in place when out == x.
-//   0: relu(x)^2    1: tanh(x)    2: 0.5 x (1 + tanh(sqrt(2/pi) (x + 0.044715 x^3)))    3: x sigmoid(x)
-//   4: exp(-exp(x + b[c])): a decay in (0, 1) from its doubly logarithmic form, with a bias per column
-// Arithmetic in float32; the input and the output each float32 or bfloat16.
-#define ACT_RELU2 0
-#define ACT_TANH 1
-#define ACT_GELU_TANH 2
-#define ACT_SILU 3
-#define ACT_NEG_EXP_EXP 4
+// f by its number (rb_activate in common.cuh).  Arithmetic in float32; the input and the output each float32 or bfloat16.
 
 template <typename TI, typename TO>
 __global__ void activation_kernel(const TI* __restrict__ x, long long ldx, TO* __restrict__ out, long long ldo, int op,
@@ -430,13 +423,7 @@ __global__ void activation_kernel(const TI* __restrict__ x, long long ldx, TO* _
         const long long r = e / cols;
         const int c = (int)(e - r * cols);
         const float v = to_f32(x[r * ldx + c]);
-        float y;
-        if (op == ACT_RELU2) { const float p = fmaxf(v, 0.f); y = p * p; }
-        else if (op == ACT_TANH) y = tanhf(v);
-        else if (op == ACT_GELU_TANH) y = 0.5f * v * (1.0f + tanhf(0.7978845608028654f * (v + 0.044715f * v * v * v)));
-        else if (op == ACT_SILU) y = v / (1.0f + expf(-v));
-        else y = expf(-expf(v + (bias ? load_as_f32(bias, bias_dtype, c) : 0.f)));
-        out[r * ldo + c] = from_f32<TO>(y);
+        out[r * ldo + c] = from_f32<TO>(rb_activate(op, v, bias, bias_dtype, (size_t)c));
     }
 }
 

@@ -56,6 +56,9 @@ struct SkinnyFused {
     float offset;
     float* ssq_out;           // residual form: [8, ssq_ld], this CTA writes column blockIdx.x; or null
     int ssq_ld;
+    int act;                  // plain form: 0, or 1 + the number of an activation (rb_activate) applied to every output
+    const void* act_bias;     // its bias per output column, or null
+    int act_bias_dtype;
 };
 
 template <int MT, int U>
@@ -181,6 +184,9 @@ gemm_skinny_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, TOut*
                                             v * (F.offset + load_as_f32(F.norm_w, F.norm_w_dtype, (size_t)(n0 + n))));
                     } else {
                         if constexpr (FUSED == 1) s *= s_scale[m];
+                        if constexpr (FUSED == 0) {
+                            if (F.act) s = rb_activate(F.act - 1, s, F.act_bias, F.act_bias_dtype, (size_t)(n0 + n));
+                        }
                         store_out<TOut>(out + (size_t)m * ldo + n0 + n, s);
                     }
                 }
@@ -241,10 +247,11 @@ int grid_for(int N) {
 
 template <int MT>
 int launch(const bf16* x, const bf16* w, void* out, int out_f32, int gated, int M, int N, int K, int ldx, int ldw,
-           int ldo, cudaStream_t st) {
+           int ldo, cudaStream_t st, int act = 0, const void* act_bias = nullptr, int act_bias_dtype = 0) {
     const int grid = grid_for(N);
     if (grid <= 0) return (int)cudaErrorInvalidDevice;
-    const SkinnyFused none = {};
+    SkinnyFused none = {};
+    none.act = act; none.act_bias = act_bias; none.act_bias_dtype = act_bias_dtype;
     if (gated)
         return rb_launch_pdl(gemm_skinny_kernel<MT, bf16, true, 0>, dim3(grid), dim3(SK_WARPS * 32), 0, st, x, w, (bf16*)out, M, N, K, ldx, ldw, ldo, none);
     if (out_f32)
@@ -276,7 +283,7 @@ RB_EXPORT int rb_gemm_skinny_fused(const void* x, const void* w, void* out, int 
     if (grid <= 0) return (int)cudaErrorInvalidDevice;
     if ((ssq_in != nullptr && (ssq_in_count < 1 || ssq_in_count > ssq_ld || norm_dim < 1)) || (ssq_out != nullptr && ssq_ld < grid))
         return (int)cudaErrorInvalidValue;
-    SkinnyFused F;
+    SkinnyFused F = {};
     F.ssq_in = ssq_in; F.ssq_in_count = ssq_in_count; F.norm_dim = norm_dim; F.eps = eps; F.stream = stream;
     F.norm_w = norm_w; F.norm_w_dtype = norm_w_dtype; F.offset = offset; F.ssq_out = ssq_out; F.ssq_ld = ssq_ld;
     const bf16* xp = (const bf16*)x;
@@ -301,4 +308,19 @@ RB_EXPORT int rb_gemm_skinny(const void* x, const void* w, void* out, int out_f3
     if (M <= 8) return launch<1>(xp, wp, out, out_f32, gated, M, N, K, ldx, ldw, ldo, st);
     if (M <= 16) return launch<2>(xp, wp, out, out_f32, gated, M, N, K, ldx, ldw, ldo, st);
     return launch<4>(xp, wp, out, out_f32, gated, M, N, K, ldx, ldw, ldo, st);
+}
+
+// The plain product with an activation on every output before it is stored: act is the number of one of the
+// one-argument activations (rb_activate), bias (float32 or bfloat16, [N]) the per-column bias of those that take one.
+RB_EXPORT int rb_gemm_skinny_act(const void* x, const void* w, void* out, int out_f32, int act, const void* bias,
+                                 int bias_dtype, int M, int N, int K, int ldx, int ldw, int ldo, cudaStream_t st) {
+    if (M <= 0 || N <= 0) return 0;
+    if (M > 32 || K % 8 || ldx % 8 || ldw % 8 || ((uintptr_t)x % 16) || ((uintptr_t)w % 16))
+        return (int)cudaErrorInvalidValue;
+    if (act < 0 || act > ACT_NEG_EXP_EXP) return (int)cudaErrorInvalidValue;
+    const bf16* xp = (const bf16*)x;
+    const bf16* wp = (const bf16*)w;
+    if (M <= 8) return launch<1>(xp, wp, out, out_f32, 0, M, N, K, ldx, ldw, ldo, st, act + 1, bias, bias_dtype);
+    if (M <= 16) return launch<2>(xp, wp, out, out_f32, 0, M, N, K, ldx, ldw, ldo, st, act + 1, bias, bias_dtype);
+    return launch<4>(xp, wp, out, out_f32, 0, M, N, K, ldx, ldw, ldo, st, act + 1, bias, bias_dtype);
 }

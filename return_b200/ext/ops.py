@@ -91,6 +91,8 @@ def core() -> ctypes.CDLL:
         lib.rb_gemm_f32.argtypes = [P, P, P, I, I, I, I, I, I, P]
         lib.rb_gemm_skinny.argtypes = [P, P, P, I, I, I, I, I, I, I, I, P]
         lib.rb_gemm_skinny.restype = c_int
+        lib.rb_gemm_skinny_act.argtypes = [P, P, P, I, I, P, I, I, I, I, I, I, I, P]
+        lib.rb_gemm_skinny_act.restype = c_int
         lib.rb_gemm_skinny_fused.argtypes = [P, P, P, I, I, I, I, I, I, I, I, P, I, I, F, P, P, I, F, P, I, P]
         lib.rb_gemm_skinny_fused.restype = c_int
         lib.rb_gemm_skinny_ctas.argtypes = [I]
@@ -280,15 +282,23 @@ SKINNY_MAX_ROWS = 8             # what the engine gives it: beyond 8 rows the li
                                 # 16 rows and 106 at 32, for N = 24576, K = 4096)
 
 
-def gemm_skinny(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, gated: bool = False) -> None:
+def gemm_skinny(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, gated: bool = False, act: Optional[str] = None,
+                bias: Optional[torch.Tensor] = None) -> None:
     """out[M, N] = x[M, K] @ w[N, K]^T for M <= 32 in bfloat16: the weight-streaming kernel of decode steps
     (the engine uses it up to 8 rows).
-    ``gated``: w holds gate and up rows interleaved in blocks of 8; out[M, N/2] = silu(gate) * up."""
+    ``gated``: w holds gate and up rows interleaved in blocks of 8; out[M, N/2] = silu(gate) * up.
+    ``act``: one of ``ACTIVATIONS`` applied to the float32 sums before they are stored (``bias``: its bias per column)."""
     M, K = x.shape
     N = w.shape[0]
     assert x.dtype == w.dtype == torch.bfloat16 and out.dtype in (torch.bfloat16, torch.float32)
     assert w.shape[1] == K and out.shape == (M, N // 2 if gated else N) and M <= SKINNY_KERNEL_MAX_ROWS
     assert x.stride(1) == 1 and w.stride(1) == 1 and out.stride(1) == 1
+    if act is not None:
+        assert not gated and (bias is None or (act == "neg_exp_exp" and bias.numel() == N and bias.is_contiguous()))
+        _check(core().rb_gemm_skinny_act(_ptr(x), _ptr(w), _ptr(out), 1 if out.dtype == torch.float32 else 0,
+                                         ACTIVATIONS[act], _ptr(bias), dtype_code(bias.dtype) if bias is not None else F32,
+                                         M, N, K, x.stride(0), w.stride(0), out.stride(0), _stream()), "gemm_skinny_act")
+        return
     _check(core().rb_gemm_skinny(_ptr(x), _ptr(w), _ptr(out), 1 if out.dtype == torch.float32 else 0,
                                  1 if gated else 0, M, N, K, x.stride(0), w.stride(0), out.stride(0), _stream()),
            "gemm_skinny")
@@ -512,23 +522,29 @@ def gemm_tc5_bmn(x: torch.Tensor, b: torch.Tensor, out: torch.Tensor, bn: int = 
                                      _ptr(tc5_status(x.device)), _stream()), "gemm_tc5_bmn")
 
 
-def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
+def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, act: Optional[str] = None,
+           bias: Optional[torch.Tensor] = None) -> None:
     """out = x @ w^T.  float32: the engine's own FFMA kernel.  bfloat16 with up to 8 rows: the
     engine's weight-streaming kernel.  bfloat16 with more rows: cuBLAS with float32 accumulation.
-    The output is bfloat16 or float32 (``out``'s dtype)."""
+    The output is bfloat16 or float32 (``out``'s dtype).  ``act``: out = f(x @ w^T) for one of ``ACTIVATIONS``
+    (``bias``: its bias per column): in the weight-streaming kernel's epilogue, else a launch of its own in place."""
     if x.dtype == torch.float32:
         gemm_f32(x, w, out)
+        if act is not None:
+            activation(out, out, act, bias)
         return
     if not x.is_cuda:
         raise KernelError("the engine's kernels run on a CUDA device only; got a CPU tensor")
     assert x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
     if skinny_ok(x, w):
-        gemm_skinny(x, w, out)
+        gemm_skinny(x, w, out, act=act, bias=bias)
         return
     if out.dtype == torch.float32:
         torch.mm(x, w.t(), out_dtype=torch.float32, out=out)
     else:
         torch.mm(x, w.t(), out=out)
+    if act is not None:
+        activation(out, out, act, bias)
 
 
 # ------------------------------------------------------------------------------- attention

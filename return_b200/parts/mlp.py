@@ -40,8 +40,8 @@ class SwiGLU(FeedForward):
 
 @FEED_FORWARDS.register("dense_mlp")
 class DenseMLP(FeedForward):
-    """y = down( act(up(x)) ) without a gate (``DenseMLPSpec``); the activation is applied in place on the first
-    product's output, in float32 arithmetic."""
+    """y = down( act(up(x)) ) without a gate (``DenseMLPSpec``); the activation is applied to the first
+    product's float32 sums in the weight-streaming kernel's epilogue (few rows), or in place on its output."""
 
     def __init__(self, spec, env):
         super().__init__(spec, env)
@@ -57,8 +57,7 @@ class DenseMLP(FeedForward):
         s = self.spec
         T = x.shape[0]
         act = work_buffer(ctx, "dense_mlp.act", (T, s.intermediate_size), x.dtype, x.device)
-        ops.linear(x, self.p_up, act)
-        ops.activation(act, act, s.activation)
+        ops.linear(x, self.p_up, act, act=s.activation)
         y = work_buffer(ctx, "dense_mlp.y", (T, s.hidden_size), x.dtype, x.device)
         ops.linear(act, self.p_down, y)
         return y

@@ -320,11 +320,9 @@ class TimeMix(_StateMixer):
         for i, w in enumerate((self.p_r, self.p_k, self.p_v, self.p_g)):
             ops.linear(mixes[i], w, proj[i])
         low = ctx.buffer("time_mix.low", (T, s.decay_rank), dt, dev)
-        ops.linear(mixes[4], self.p_decay_down, low)
-        ops.activation(low, low, "tanh")
+        ops.linear(mixes[4], self.p_decay_down, low, act="tanh")
         decay = ctx.buffer("time_mix.decay", (T, HD), torch.float32, dev)
-        ops.linear(low, self.p_decay_up, decay)
-        ops.activation(decay, decay, "neg_exp_exp", bias=self.p_decay_bias)
+        ops.linear(low, self.p_decay_up, decay, act="neg_exp_exp", bias=self.p_decay_bias)
         o = ctx.buffer("time_mix.o", (T, HD), torch.float32, dev)
         self._scan(ops.SCAN_BONUS, proj[0], proj[1], proj[2], decay, None, ctx, o, self.H, self._bonus32, True,
                    self._pieces(b) if dt != torch.float32 else None)

@@ -248,6 +248,29 @@ def test_activations(dtype):
     assert torch.allclose(out.cpu().double(), torch.exp(-torch.exp(x.float().double() + bias.double())), rtol=1e-5, atol=1e-6)
 
 
+@pytest.mark.parametrize("rows", [1, 5, 8, 13, 40])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_product_with_an_activation_behind_it(rows, dtype):
+    """``ops.linear(..., act=)``: few bfloat16 rows take the activation in the product's epilogue, more rows and float32
+    in a launch of their own; both against the activation of the float64 product."""
+    from return_b200.ext import ops
+    g = torch.Generator().manual_seed(rows)
+    K, N = 72, 52
+    x = (torch.randn((rows, K), generator=g)).to(dtype)
+    w = (torch.randn((N, K), generator=g) * K ** -0.5).to(dtype)
+    bias = torch.randn(N, generator=g)
+    z = x.double() @ w.double().t()
+    cases = (("relu2", plain.relu_squared(z), None), ("tanh", torch.tanh(z), None), ("silu", torch.nn.functional.silu(z), None),
+             ("neg_exp_exp", torch.exp(-torch.exp(z + bias.double())), bias))
+    for kind, want, b in cases:
+        for out_dtype in (dtype, torch.float32):
+            out = torch.empty((rows, N), dtype=out_dtype, device="cuda")
+            ops.linear(x.cuda(), w.cuda(), out, act=kind, bias=None if b is None else b.cuda())
+            tol = dict(rtol=1e-4, atol=1e-5) if dtype == torch.float32 else \
+                (dict(rtol=2e-2, atol=2e-2) if out_dtype == torch.bfloat16 else dict(rtol=1e-4, atol=1e-5))
+            assert torch.allclose(out.cpu().double(), want, **tol), (kind, rows, out_dtype)
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_blends_with_the_token_before(dtype):
     """Three segments: one from a request that kept a last input, one new (its slot holds zeros), one of a single token;
