@@ -459,12 +459,12 @@ hyper_read_norm_kernel(const float* __restrict__ streams, const float* __restric
                        const void* __restrict__ w, int w_dtype, float eps, float offset, TA* __restrict__ out, int H) {
     extern __shared__ float hyper_smem[];                  // H floats, then 33 for the sum
     float* scratch = hyper_smem + H;
+    float coef[S];                                         // parameters: nobody's output, read ahead of the wait
+#pragma unroll
+    for (int s = 0; s < S; ++s) coef[s] = a ? a[s] : 1.0f;
     pdl_wait();
     const size_t t = rows ? (size_t)rows[blockIdx.x] : (size_t)blockIdx.x;
     const float* x = streams + t * S * H;
-    float coef[S];
-#pragma unroll
-    for (int s = 0; s < S; ++s) coef[s] = a ? a[s] : 1.0f;
     float ss = 0.f;
     for (int i = threadIdx.x; i < H; i += blockDim.x) {
         float u = 0.f;
@@ -487,10 +487,9 @@ hyper_write_kernel(float* __restrict__ streams, const TY* __restrict__ y, const 
                    int w_dtype, float eps, float offset, TA* __restrict__ out, int H) {
     extern __shared__ float hyper_smem[];
     float* scratch = hyper_smem + H;
-    pdl_wait();
     const size_t t = blockIdx.x;
     float* x = streams + t * S * H;
-    float mix[S][S], bo[S], an[S];
+    float mix[S][S], bo[S], an[S];                         // parameters: nobody's output, read ahead of the wait
 #pragma unroll
     for (int s = 0; s < S; ++s) {
         bo[s] = b[s];
@@ -498,6 +497,7 @@ hyper_write_kernel(float* __restrict__ streams, const TY* __restrict__ y, const 
 #pragma unroll
         for (int r = 0; r < S; ++r) mix[s][r] = m[s * S + r];
     }
+    pdl_wait();
     float ss = 0.f;
     for (int i = threadIdx.x; i < H; i += blockDim.x) {
         float old[S];

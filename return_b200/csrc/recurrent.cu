@@ -929,10 +929,65 @@ __global__ void gated_part_norm_kernel(const float* __restrict__ y, const TA* __
     }
 }
 
+// The same for parts of 256 elements or more: one CTA of 128 threads a part, the first eight gated values of a thread
+// kept in registers between the sum of squares and the store.  Which of the two kernels runs depends on the part's size
+// alone, never on the number of rows, so a row's sums are added in one order whatever else the step holds.
+#define PART_NORM_WIDE_FROM 256
+template <typename TA>
+__global__ void __launch_bounds__(128)
+gated_part_norm_wide_kernel(const float* __restrict__ y, const TA* __restrict__ z, int z_ld,
+                            const void* __restrict__ w, int w_dtype, float eps, TA* __restrict__ out, int parts, int size) {
+    __shared__ float scratch[33];
+    constexpr int HOLD = 8;
+    pdl_wait();
+    const int row = blockIdx.x, tid = threadIdx.x;
+    const int t = row / parts, p = row - t * parts;
+    const float* yr = y + (size_t)row * size;
+    const TA* zr = z + (size_t)t * z_ld + (size_t)p * size;
+    float held[HOLD];
+    float ss = 0.f;
+#pragma unroll
+    for (int j = 0; j < HOLD; ++j) {
+        const int i = tid + j * 128;
+        held[j] = 0.f;
+        if (i < size) {
+            const float g = to_f32(zr[i]);
+            held[j] = yr[i] * (g / (1.0f + expf(-g)));
+            ss = fmaf(held[j], held[j], ss);
+        }
+    }
+    for (int i = tid + HOLD * 128; i < size; i += 128) {
+        const float g = to_f32(zr[i]);
+        const float v = yr[i] * (g / (1.0f + expf(-g)));
+        ss = fmaf(v, v, ss);
+    }
+    ss = block_sum(ss, scratch);
+    pdl_trigger_late();
+    const float rstd = 1.0f / sqrtf(ss / (float)size + eps);
+    TA* o = out + (size_t)row * size;
+#pragma unroll
+    for (int j = 0; j < HOLD; ++j) {
+        const int i = tid + j * 128;
+        if (i < size) o[i] = from_f32<TA>(held[j] * rstd * load_as_f32(w, w_dtype, (size_t)p * size + i));
+    }
+    for (int i = tid + HOLD * 128; i < size; i += 128) {
+        const float g = to_f32(zr[i]);
+        const float v = yr[i] * (g / (1.0f + expf(-g)));
+        o[i] = from_f32<TA>(v * rstd * load_as_f32(w, w_dtype, (size_t)p * size + i));
+    }
+}
+
 RB_EXPORT int rb_gated_part_norm(const float* y, const void* z, int z_ld, const void* w, int w_dtype, float eps, void* out,
                                  int act_dtype, int T, int parts, int size, cudaStream_t st) {
     const int rows = T * parts;
     if (rows <= 0) return 0;
+    if (size >= PART_NORM_WIDE_FROM) {
+        if (act_dtype == RB_F32)
+            return rb_launch_pdl(gated_part_norm_wide_kernel<float>, dim3(rows), dim3(128), 0, st, y, (const float*)z, z_ld, w,
+                                 w_dtype, eps, (float*)out, parts, size);
+        return rb_launch_pdl(gated_part_norm_wide_kernel<bf16>, dim3(rows), dim3(128), 0, st, y, (const bf16*)z, z_ld, w, w_dtype,
+                             eps, (bf16*)out, parts, size);
+    }
     const int blocks = (rows + 3) / 4;
     if (act_dtype == RB_F32)
         return rb_launch_pdl(gated_part_norm_kernel<float>, dim3(blocks), dim3(128), 0, st, y, (const float*)z, z_ld, w, w_dtype, eps,

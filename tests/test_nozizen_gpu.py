@@ -340,7 +340,7 @@ def test_convolution_steps_and_decays_of_a_state_space_scan(taps):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("parts,n", [(1, 40), (3, 24), (6, 48), (2, 66)])
+@pytest.mark.parametrize("parts,n", [(1, 40), (3, 24), (6, 48), (2, 66), (2, 512), (3, 900), (1, 1500), (2, 2500)])
 def test_gate_then_norm_over_equal_parts(parts, n, dtype):
     from return_b200.ext import ops
     g = torch.Generator().manual_seed(parts)
