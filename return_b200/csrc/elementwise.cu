@@ -453,12 +453,52 @@ RB_EXPORT int rb_activation(const void* x, long long ldx, int x_dtype, void* out
 // of its columns in registers, S <= HYPER_MAX_STREAMS.  With `rows` the read kernel takes only the listed rows.
 #define HYPER_MAX_STREAMS 8
 
-template <typename TA, int S>
+// VEC columns a thread and step (4 when H is a multiple of 4: 16-byte loads and stores of the streams; else 1).  Which
+// columns a thread sums depends on H alone, so a row's sum of squares is added in one order whatever the step holds.
+template <int VEC> __device__ __forceinline__ void hyper_load(const float* p, float (&v)[VEC]) {
+    if constexpr (VEC == 4) { const float4 q = *reinterpret_cast<const float4*>(p); v[0] = q.x; v[1] = q.y; v[2] = q.z; v[3] = q.w; }
+    else v[0] = *p;
+}
+template <int VEC> __device__ __forceinline__ void hyper_load(const bf16* p, float (&v)[VEC]) {
+    if constexpr (VEC == 4) {
+        const uint2 q = *reinterpret_cast<const uint2*>(p);
+        const float2 lo = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&q.x));
+        const float2 hi = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&q.y));
+        v[0] = lo.x; v[1] = lo.y; v[2] = hi.x; v[3] = hi.y;
+    } else v[0] = to_f32(*p);
+}
+template <int VEC> __device__ __forceinline__ void hyper_store(float* p, const float (&v)[VEC]) {
+    if constexpr (VEC == 4) *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+    else *p = v[0];
+}
+template <int VEC> __device__ __forceinline__ void hyper_store(bf16* p, const float (&v)[VEC]) {
+    if constexpr (VEC == 4) {
+        const __nv_bfloat162 lo = __floats2bfloat162_rn(v[0], v[1]), hi = __floats2bfloat162_rn(v[2], v[3]);
+        uint2 q;
+        q.x = *reinterpret_cast<const unsigned*>(&lo);
+        q.y = *reinterpret_cast<const unsigned*>(&hi);
+        *reinterpret_cast<uint2*>(p) = q;
+    } else *p = __float2bfloat16_rn(v[0]);
+}
+
+// The normed rows from the sums a row left in shared memory.
+template <typename TA, int VEC>
+__device__ __forceinline__ void hyper_normed_rows(const float* u, float rstd, const void* w, int w_dtype, float offset,
+                                                  TA* out_row, int H) {
+    for (int i = threadIdx.x * VEC; i < H; i += blockDim.x * VEC) {
+        float o[VEC];
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) o[e] = u[i + e] * rstd * (offset + load_as_f32(w, w_dtype, (size_t)(i + e)));
+        hyper_store<VEC>(out_row + i, o);
+    }
+}
+
+template <typename TA, int S, int VEC>
 __global__ void __launch_bounds__(256)
 hyper_read_norm_kernel(const float* __restrict__ streams, const float* __restrict__ a, const int* __restrict__ rows,
                        const void* __restrict__ w, int w_dtype, float eps, float offset, TA* __restrict__ out, int H) {
-    extern __shared__ float hyper_smem[];                  // H floats, then 33 for the sum
-    float* scratch = hyper_smem + H;
+    extern __shared__ __align__(16) float hyper_smem[];    // H floats, then 33 for the sum
+    float* scratch = hyper_smem + ((H + 3) & ~3);
     float coef[S];                                         // parameters: nobody's output, read ahead of the wait
 #pragma unroll
     for (int s = 0; s < S; ++s) coef[s] = a ? a[s] : 1.0f;
@@ -466,27 +506,32 @@ hyper_read_norm_kernel(const float* __restrict__ streams, const float* __restric
     const size_t t = rows ? (size_t)rows[blockIdx.x] : (size_t)blockIdx.x;
     const float* x = streams + t * S * H;
     float ss = 0.f;
-    for (int i = threadIdx.x; i < H; i += blockDim.x) {
-        float u = 0.f;
+    for (int i = threadIdx.x * VEC; i < H; i += blockDim.x * VEC) {
+        float old[S][VEC];
 #pragma unroll
-        for (int s = 0; s < S; ++s) u = fmaf(coef[s], x[(size_t)s * H + i], u);
-        hyper_smem[i] = u;
-        ss = fmaf(u, u, ss);
+        for (int s = 0; s < S; ++s) hyper_load<VEC>(x + (size_t)s * H + i, old[s]);
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) {
+            float u = 0.f;
+#pragma unroll
+            for (int s = 0; s < S; ++s) u = fmaf(coef[s], old[s][e], u);
+            hyper_smem[i + e] = u;
+            ss = fmaf(u, u, ss);
+        }
     }
     ss = block_sum(ss, scratch);
     pdl_trigger_late();
     const float rstd = 1.0f / sqrtf(ss / (float)H + eps);
-    for (int i = threadIdx.x; i < H; i += blockDim.x)
-        out[(size_t)blockIdx.x * H + i] = from_f32<TA>(hyper_smem[i] * rstd * (offset + load_as_f32(w, w_dtype, i)));
+    hyper_normed_rows<TA, VEC>(hyper_smem, rstd, w, w_dtype, offset, out + (size_t)blockIdx.x * H, H);
 }
 
-template <typename TA, typename TY, int S>
+template <typename TA, typename TY, int S, int VEC>
 __global__ void __launch_bounds__(256)
 hyper_write_kernel(float* __restrict__ streams, const TY* __restrict__ y, const float* __restrict__ m,
                    const float* __restrict__ b, const float* __restrict__ a_next, const void* __restrict__ w_next,
                    int w_dtype, float eps, float offset, TA* __restrict__ out, int H) {
-    extern __shared__ float hyper_smem[];
-    float* scratch = hyper_smem + H;
+    extern __shared__ __align__(16) float hyper_smem[];
+    float* scratch = hyper_smem + ((H + 3) & ~3);
     const size_t t = blockIdx.x;
     float* x = streams + t * S * H;
     float mix[S][S], bo[S], an[S];                         // parameters: nobody's output, read ahead of the wait
@@ -499,38 +544,48 @@ hyper_write_kernel(float* __restrict__ streams, const TY* __restrict__ y, const 
     }
     pdl_wait();
     float ss = 0.f;
-    for (int i = threadIdx.x; i < H; i += blockDim.x) {
-        float old[S];
+    for (int i = threadIdx.x * VEC; i < H; i += blockDim.x * VEC) {
+        float old[S][VEC], yv[VEC], u[VEC];
 #pragma unroll
-        for (int s = 0; s < S; ++s) old[s] = x[(size_t)s * H + i];
-        const float yv = to_f32(y[t * H + i]);
-        float u = 0.f;
+        for (int s = 0; s < S; ++s) hyper_load<VEC>(x + (size_t)s * H + i, old[s]);
+        hyper_load<VEC>(y + t * H + i, yv);
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) u[e] = 0.f;
 #pragma unroll
         for (int r = 0; r < S; ++r) {
-            float v = bo[r] * yv;
+            float v[VEC];
 #pragma unroll
-            for (int s = 0; s < S; ++s) v = fmaf(mix[s][r], old[s], v);
-            x[(size_t)r * H + i] = v;
-            u = fmaf(an[r], v, u);
+            for (int e = 0; e < VEC; ++e) {
+                v[e] = bo[r] * yv[e];
+#pragma unroll
+                for (int s = 0; s < S; ++s) v[e] = fmaf(mix[s][r], old[s][e], v[e]);
+                u[e] = fmaf(an[r], v[e], u[e]);
+            }
+            hyper_store<VEC>(x + (size_t)r * H + i, v);
         }
         if (out) {
-            hyper_smem[i] = u;
-            ss = fmaf(u, u, ss);
+#pragma unroll
+            for (int e = 0; e < VEC; ++e) {
+                hyper_smem[i + e] = u[e];
+                ss = fmaf(u[e], u[e], ss);
+            }
         }
     }
     if (!out) return;
     ss = block_sum(ss, scratch);
     pdl_trigger_late();
     const float rstd = 1.0f / sqrtf(ss / (float)H + eps);
-    for (int i = threadIdx.x; i < H; i += blockDim.x)
-        out[t * H + i] = from_f32<TA>(hyper_smem[i] * rstd * (offset + load_as_f32(w_next, w_dtype, i)));
+    hyper_normed_rows<TA, VEC>(hyper_smem, rstd, w_next, w_dtype, offset, out + t * H, H);
 }
 
 template <typename TA, int S>
 static int hyper_read_launch(const float* streams, const float* a, const int* rows, const void* w, int w_dtype, float eps,
                              float offset, void* out, int n, int H, cudaStream_t st) {
-    const size_t smem = (size_t)(H + 33) * sizeof(float);
-    return rb_launch_pdl(hyper_read_norm_kernel<TA, S>, dim3(n), dim3(256), smem, st, streams, a, rows, w, w_dtype, eps, offset,
+    const size_t smem = (size_t)(((H + 3) & ~3) + 33) * sizeof(float);
+    if (H % 4 == 0 && (uintptr_t)streams % 16 == 0 && (uintptr_t)out % 16 == 0)
+        return rb_launch_pdl(hyper_read_norm_kernel<TA, S, 4>, dim3(n), dim3(256), smem, st, streams, a, rows, w, w_dtype, eps,
+                             offset, (TA*)out, H);
+    return rb_launch_pdl(hyper_read_norm_kernel<TA, S, 1>, dim3(n), dim3(256), smem, st, streams, a, rows, w, w_dtype, eps, offset,
                          (TA*)out, H);
 }
 
@@ -538,8 +593,11 @@ template <typename TA, typename TY, int S>
 static int hyper_write_launch(float* streams, const void* y, const float* m, const float* b, const float* a_next,
                               const void* w_next, int w_dtype, float eps, float offset, void* out, int T, int H,
                               cudaStream_t st) {
-    const size_t smem = (size_t)(H + 33) * sizeof(float);
-    return rb_launch_pdl(hyper_write_kernel<TA, TY, S>, dim3(T), dim3(256), smem, st, streams, (const TY*)y, m, b, a_next, w_next,
+    const size_t smem = (size_t)(((H + 3) & ~3) + 33) * sizeof(float);
+    if (H % 4 == 0 && (uintptr_t)streams % 16 == 0 && (uintptr_t)y % 16 == 0 && (uintptr_t)out % 16 == 0)
+        return rb_launch_pdl(hyper_write_kernel<TA, TY, S, 4>, dim3(T), dim3(256), smem, st, streams, (const TY*)y, m, b, a_next,
+                             w_next, w_dtype, eps, offset, (TA*)out, H);
+    return rb_launch_pdl(hyper_write_kernel<TA, TY, S, 1>, dim3(T), dim3(256), smem, st, streams, (const TY*)y, m, b, a_next, w_next,
                          w_dtype, eps, offset, (TA*)out, H);
 }
 
@@ -554,7 +612,7 @@ static int hyper_write_launch(float* streams, const void* y, const float* m, con
 RB_EXPORT int rb_hyper_read_norm(const float* streams, const float* a, const int* rows, const void* w, int w_dtype, float eps,
                                  float offset, void* out, int act_dtype, int n, int S, int H, cudaStream_t st) {
     if (n <= 0) return 0;
-    if ((size_t)(H + 33) * sizeof(float) > 48 * 1024) return (int)cudaErrorInvalidValue;
+    if ((size_t)(H + 36) * sizeof(float) > 48 * 1024) return (int)cudaErrorInvalidValue;
     if (act_dtype == RB_F32) {
 #define CALL(N) hyper_read_launch<float, N>(streams, a, rows, w, w_dtype, eps, offset, out, n, H, st)
         HYPER_BY_STREAMS(CALL)
@@ -569,7 +627,7 @@ RB_EXPORT int rb_hyper_write(float* streams, const void* y, int y_f32, const flo
                              const void* w_next, int w_dtype, float eps, float offset, void* out, int act_dtype, int T,
                              int S, int H, cudaStream_t st) {
     if (T <= 0) return 0;
-    if ((size_t)(H + 33) * sizeof(float) > 48 * 1024) return (int)cudaErrorInvalidValue;
+    if ((size_t)(H + 36) * sizeof(float) > 48 * 1024) return (int)cudaErrorInvalidValue;
     if (act_dtype == RB_F32) {                             // the 32-bit path: y is float32 as well
 #define CALL(N) hyper_write_launch<float, float, N>(streams, y, m, b, a_next, w_next, w_dtype, eps, offset, out, T, H, st)
         HYPER_BY_STREAMS(CALL)

@@ -824,7 +824,7 @@ token_shift_mix_kernel(const TA* __restrict__ x, int ld, const void* __restrict_
     const bool first = t == cu_q[seg];
     const float* kept = state + (long long)seg_slot[seg] * state_stride + shift_off;
     const TA* cur = x + (size_t)t * ld;
-    for (int i = threadIdx.x; i < W; i += blockDim.x) {
+    for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < W; i += gridDim.y * blockDim.x) {   // a column a thread
         const float c = to_f32(cur[i]);
         const float d = (first ? kept[i] : to_f32(x[(size_t)(t - 1) * ld + i])) - c;
         for (int n = 0; n < N; ++n)
@@ -836,11 +836,12 @@ RB_EXPORT int rb_token_shift_mix(const void* x, int ld, const void* mu, int mu_d
                                  long long state_stride, int shift_off, const int* tok_seg, const int* cu_q,
                                  const int* seg_slot, void* out, int act_dtype, int T, int W, cudaStream_t st) {
     if (T <= 0 || N <= 0) return 0;
-    const int threads = W >= 1024 ? 256 : 128;
+    const int threads = 128;
+    const int across = (W + threads - 1) / threads < 65535 ? (W + threads - 1) / threads : 65535;
     if (act_dtype == RB_F32)
-        return rb_launch_pdl(token_shift_mix_kernel<float>, dim3(T), dim3(threads), 0, st, (const float*)x, ld, mu, mu_dtype, N,
+        return rb_launch_pdl(token_shift_mix_kernel<float>, dim3(T, across), dim3(threads), 0, st, (const float*)x, ld, mu, mu_dtype, N,
                              state, state_stride, shift_off, tok_seg, cu_q, seg_slot, (float*)out, T, W);
-    return rb_launch_pdl(token_shift_mix_kernel<bf16>, dim3(T), dim3(threads), 0, st, (const bf16*)x, ld, mu, mu_dtype, N, state,
+    return rb_launch_pdl(token_shift_mix_kernel<bf16>, dim3(T, across), dim3(threads), 0, st, (const bf16*)x, ld, mu, mu_dtype, N, state,
                          state_stride, shift_off, tok_seg, cu_q, seg_slot, (bf16*)out, T, W);
 }
 

@@ -187,7 +187,7 @@ def _tol(dtype):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("S,H", [(1, 40), (3, 72), (4, 320), (8, 24)])
+@pytest.mark.parametrize("S,H", [(1, 40), (3, 72), (4, 320), (8, 24), (2, 38), (3, 1026), (4, 4096), (8, 2048)])
 def test_streams_read_and_write(S, H, dtype):
     """The read (weighted sum of the streams, normed), the write (all streams at once from the old ones), the write with
     the next read in the same kernel, and the plain sum that goes to the final norm, against the plain sublayer."""
