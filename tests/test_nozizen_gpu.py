@@ -187,7 +187,7 @@ def _tol(dtype):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("S,H", [(1, 40), (3, 72), (4, 320), (8, 24), (2, 38), (3, 1026), (4, 4096), (8, 2048)])
+@pytest.mark.parametrize("S,H", [(1, 40), (3, 72), (4, 296), (8, 24), (2, 38), (3, 1026), (4, 4096), (8, 2048)])
 def test_streams_read_and_write(S, H, dtype):
     """The read (weighted sum of the streams, normed), the write (all streams at once from the old ones), the write with
     the next read in the same kernel, and the plain sum that goes to the final norm, against the plain sublayer."""
@@ -390,7 +390,7 @@ def test_scan_with_row_decays_and_a_bonus(H, D):
     assert not state[1].any()                                       # the slot of no request stayed as it was
 
 
-@pytest.mark.parametrize("H,G,N,P", [(4, 2, 10, 6), (1, 1, 7, 33), (6, 3, 136, 8), (2, 2, 48, 48)])
+@pytest.mark.parametrize("H,G,N,P", [(4, 2, 10, 6), (1, 1, 7, 33), (6, 3, 136, 8), (2, 2, 40, 40)])
 def test_scan_of_a_state_space(H, G, N, P):
     """M <- a M + dt B x^T, y = M^T C + D x, heads sharing the maps of their group; a prompt, then token by token."""
     from return_b200.ext import ops
@@ -420,7 +420,7 @@ def test_scan_of_a_state_space(H, G, N, P):
     assert torch.allclose(got.double(), want.reshape(T, H * P), rtol=1e-4, atol=1e-4)
 
 
-@pytest.mark.parametrize("E,top", [(16, 4), (5, 2), (7, 1), (3, 3), (35, 4), (64, 8)])
+@pytest.mark.parametrize("E,top", [(12, 4), (5, 2), (7, 1), (3, 3), (35, 4), (64, 8)])
 def test_router_with_a_bias_weighs_the_chosen_logits_only(E, top):
     from return_b200.ext import ops
     g = torch.Generator().manual_seed(E * 10 + top)
