@@ -99,6 +99,12 @@ def _register_builtin() -> None:
         name="Nozizen", model_type="nozizen", config_cls=NozizenConfig,
         decoder_spec=nozizen.decoder_spec, weight_sources=nozizen.weight_sources,
         ignorable_tensors=nozizen.ignorable_tensors, checkpoint_shapes=nozizen.checkpoint_shapes))
+    from ..models import duvadra
+    from .duvadra_config import DuvadraConfig
+    register_architecture(Architecture(
+        name="Duvadra", model_type="duvadra", config_cls=DuvadraConfig,
+        decoder_spec=duvadra.decoder_spec, weight_sources=duvadra.weight_sources,
+        ignorable_tensors=duvadra.ignorable_tensors, checkpoint_shapes=duvadra.checkpoint_shapes))
 
 
 _register_builtin()

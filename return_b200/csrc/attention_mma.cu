@@ -13,6 +13,10 @@
 // to absolute positions (so a row's arithmetic in the prefill kernel does not depend on how the
 // prompt was cut), and a sliding window bounds the keys from below.
 //
+// The kernels with MOD = true take a ScoreMod: keys bounded from below by the start of the query's own block of
+// `chunk` positions (instead of a window), scores capped softly (cap * tanh(s / cap)) and a penalty per head that
+// grows with the distance, slopes[h] * (i - j), taken off before the softmax.
+//
 // K and V of one layer: [num_pages, Hkv, P, D] bfloat16.  Shared-memory tiles are [rows][D] with
 // the 16-byte chunks of a row XOR-swizzled by the row index, which keeps ldmatrix conflict-free.
 #include "common.cuh"
@@ -80,6 +84,20 @@ __device__ __forceinline__ void mma_bf16(float (&c)[4], const unsigned (&a)[4], 
 __device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
     __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<unsigned*>(&v);
+}
+
+// What the MOD kernels do to a score between the product and the softmax.
+struct ScoreMod {
+    float scale;               // the natural scale (the plain kernels fold log2(e) into theirs)
+    float softcap;             // 0: none
+    const float* slopes;       // [Hq] or null
+    int chunk;                 // 0: none
+};
+__device__ __forceinline__ float mod_score(float dot, const ScoreMod& sm, float slope, int dist) {
+    float v = dot * sm.scale;
+    if (sm.softcap > 0.f) v = sm.softcap * tanhf(v / sm.softcap);
+    v = fmaf(-slope, (float)dist, v);
+    return v * LOG2E;
 }
 
 // Position -> (block, row in page).  Page sizes are powers of two in practice; any size works.
@@ -150,13 +168,14 @@ __device__ __forceinline__ void load_kv_rows(bf16* tile, const bf16* pool, const
 constexpr int PF_M = 64;      // query rows per CTA (4 warps x 16)
 constexpr int PF_N = 64;      // keys per tile
 
+template <bool MOD>
 __global__ void __launch_bounds__(128)
 attn_prefill_kernel(const bf16* __restrict__ q, int ld, const bf16* __restrict__ kpool,
                     const bf16* __restrict__ vpool, const int* __restrict__ tiles,
                     const int* __restrict__ cu_q, const int* __restrict__ seg_pos0,
                     const int* __restrict__ block_table, int bt_stride, int page_size,
                     bf16* __restrict__ out, int Hq, int Hkv, float scale_log2, int window,
-                    const float* __restrict__ sink) {
+                    const float* __restrict__ sink, ScoreMod sm) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
     bf16* sQ = reinterpret_cast<bf16*>(smem_raw);
     bf16* sK = sQ + PF_M * D;                 // two stages
@@ -172,7 +191,8 @@ attn_prefill_kernel(const bf16* __restrict__ q, int ld, const bf16* __restrict__
     const int m_rows = min(PF_M, cu_q[seg + 1] - q_begin - row0);
     const int p0 = seg_pos0[seg] + row0;      // position of the tile's first query
     const int p_last = p0 + m_rows - 1;
-    const int lo_min = window > 0 ? max(0, p0 - window + 1) : 0;
+    const int chunk = MOD ? sm.chunk : 0;
+    const int lo_min = window > 0 ? max(0, p0 - window + 1) : chunk > 0 ? (p0 / chunk) * chunk : 0;
     const int jt_begin = lo_min / PF_N, jt_end = p_last / PF_N;
     const Paging pg(page_size);
     const StagedTable bt = stage_table(sBT, block_table + (size_t)seg * bt_stride, pg.block(lo_min), pg.block(p_last), tid, 128);
@@ -196,6 +216,9 @@ attn_prefill_kernel(const bf16* __restrict__ q, int ld, const bf16* __restrict__
     const int wrow = warp * 16;
     const bool warp_active = wrow < m_rows;
     const int pos_r0 = p0 + wrow + g, pos_r1 = pos_r0 + 8;          // positions of this thread's two rows
+    const int lo_r0 = chunk > 0 ? (pos_r0 / chunk) * chunk : 0, lo_r1 = chunk > 0 ? (pos_r1 / chunk) * chunk : 0;
+    const int lo_warp = chunk > 0 ? ((p0 + wrow) / chunk) * chunk : 0;     // the lowest bound among the warp's rows
+    const float slope = (MOD && sm.slopes) ? sm.slopes[h] : 0.f;
 
     for (int jt = jt_begin; jt <= jt_end; ++jt) {
         const int stage = (jt - jt_begin) & 1;
@@ -216,7 +239,8 @@ attn_prefill_kernel(const bf16* __restrict__ q, int ld, const bf16* __restrict__
         const int j_base = jt * PF_N;
         // a tile that starts above the warp's last row, or ends below its first row's window, adds nothing
         const bool skip = !warp_active || j_base > p0 + wrow + 15 ||
-                          (window > 0 && j_base + PF_N - 1 <= p0 + wrow - window);
+                          (window > 0 && j_base + PF_N - 1 <= p0 + wrow - window) ||
+                          (chunk > 0 && j_base + PF_N - 1 < lo_warp);
         if (!skip) {
             const bf16* tK = sK + stage * PF_N * D;
             const bf16* tV = sV + stage * PF_N * D;
@@ -241,8 +265,8 @@ attn_prefill_kernel(const bf16* __restrict__ q, int ld, const bf16* __restrict__
                 for (int e = 0; e < 4; ++e) {
                     const int j = j_base + nt * 8 + 2 * t4 + (e & 1);
                     const int pr = (e & 2) ? pos_r1 : pos_r0;
-                    const bool vis = j <= pr && (window <= 0 || j > pr - window);
-                    const float v = vis ? s[nt][e] * scale_log2 : -INFINITY;
+                    const bool vis = j <= pr && (window <= 0 || j > pr - window) && (!MOD || j >= ((e & 2) ? lo_r1 : lo_r0));
+                    const float v = !vis ? -INFINITY : MOD ? mod_score(s[nt][e], sm, slope, pr - j) : s[nt][e] * scale_log2;
                     s[nt][e] = v;
                     if (e & 2) mx1 = fmaxf(mx1, v); else mx0 = fmaxf(mx0, v);
                 }
@@ -394,7 +418,7 @@ __device__ __forceinline__ void warp_norm_rope(const bf16* __restrict__ x, const
     }
 }
 
-template <bool FUSED>
+template <bool FUSED, bool MOD>
 __global__ void __launch_bounds__(DC_WARPS * 32)
 attn_decode_kernel(const bf16* __restrict__ q, int ld, const bf16* __restrict__ kpool,
                    const bf16* __restrict__ vpool, const int* __restrict__ dec_segs,
@@ -402,7 +426,7 @@ attn_decode_kernel(const bf16* __restrict__ q, int ld, const bf16* __restrict__ 
                    const int* __restrict__ block_table, int bt_stride, int page_size,
                    float* __restrict__ part_o, float* __restrict__ part_ml, bf16* __restrict__ out,
                    int Hq, int Hkv, int m_tiles, float scale_log2, int window, int num_splits, FusedRope fr,
-                   const float* __restrict__ sink) {
+                   const float* __restrict__ sink, ScoreMod sm) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
     bf16* sQ = reinterpret_cast<bf16*>(smem_raw);                    // 16 x D
     int* sBT = reinterpret_cast<int*>(sQ + 16 * D);                  // the block-table entries this CTA walks
@@ -424,7 +448,8 @@ attn_decode_kernel(const bf16* __restrict__ q, int ld, const bf16* __restrict__ 
     const int rows_valid = min(16, G - mt * 16);
     const int tok_row = cu_q[seg];
     const int kv_len = seg_kv_len[seg];
-    const int lo = window > 0 ? max(0, kv_len - window) : 0;        // first visible key
+    const int lo = window > 0 ? max(0, kv_len - window)              // first visible key
+                   : (MOD && sm.chunk > 0) ? ((kv_len - 1) / sm.chunk) * sm.chunk : 0;
     const int hi = kv_len - 1;                                       // the query's own position
     const int first = lo / DC_N, n_tiles = hi / DC_N - first + 1;
     const int per_split = (n_tiles + num_splits - 1) / num_splits;
@@ -569,7 +594,20 @@ attn_decode_kernel(const bf16* __restrict__ q, int ld, const bf16* __restrict__ 
             }
         }
         float mx0 = -INFINITY, mx1 = -INFINITY;
-        if (j_base >= lo && j_base + DC_N - 1 <= hi) {            // every key of the tile is visible
+        if (MOD) {
+            const float sl0 = (sm.slopes && g < rows_valid) ? sm.slopes[h0 + g] : 0.f;
+            const float sl1 = (sm.slopes && g + 8 < rows_valid) ? sm.slopes[h0 + g + 8] : 0.f;
+#pragma unroll
+            for (int nt = 0; nt < 2; ++nt) {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int j = j_base + nt * 8 + 2 * t4 + (e & 1);
+                    const float v = (j >= lo && j <= hi) ? mod_score(s[nt][e] + s2[nt][e], sm, (e & 2) ? sl1 : sl0, hi - j) : -INFINITY;
+                    s[nt][e] = v;
+                    if (e & 2) mx1 = fmaxf(mx1, v); else mx0 = fmaxf(mx0, v);
+                }
+            }
+        } else if (j_base >= lo && j_base + DC_N - 1 <= hi) {            // every key of the tile is visible
 #pragma unroll
             for (int nt = 0; nt < 2; ++nt) {
 #pragma unroll
@@ -753,21 +791,41 @@ attn_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ 
 
 RB_EXPORT int rb_attn_head_dim() { return D; }
 
+// softcap 0, slopes null and chunk 0: the plain kernel; anything else: the MOD kernel (a window and a chunk exclude
+// each other).
+RB_EXPORT int rb_attn_prefill_mod(const void* q, int ld, const void* kpool, const void* vpool, const int* tiles,
+                                  int n_tiles, const int* cu_q, const int* seg_pos0, const int* block_table,
+                                  int bt_stride, int page_size, void* out, int Hq, int Hkv, float scale,
+                                  int window, const float* sink, int chunk, float softcap, const float* slopes,
+                                  cudaStream_t st) {
+    if (n_tiles <= 0) return 0;
+    if (window > 0 && chunk > 0) return (int)cudaErrorInvalidValue;
+    const size_t smem = (size_t)(PF_M + 4 * PF_N) * D * sizeof(bf16) + BT_CAP * sizeof(int);
+    static PerDevice configured;
+    const int cfg = configured.once([&](int) {
+        cudaError_t e = cudaFuncSetAttribute(attn_prefill_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(attn_prefill_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        return e;
+    });
+    if (cfg != 0) return cfg;
+    dim3 grid(n_tiles, Hq);
+    ScoreMod sm;
+    sm.scale = scale; sm.softcap = softcap; sm.slopes = slopes; sm.chunk = chunk;
+    if (chunk > 0 || softcap > 0.f || slopes != nullptr)
+        return rb_launch_pdl(attn_prefill_kernel<true>, grid, dim3(128), smem, st, (const bf16*)q, ld, (const bf16*)kpool,
+                             (const bf16*)vpool, tiles, cu_q, seg_pos0, block_table, bt_stride, page_size, (bf16*)out,
+                             Hq, Hkv, scale * LOG2E, window, sink, sm);
+    return rb_launch_pdl(attn_prefill_kernel<false>, grid, dim3(128), smem, st, (const bf16*)q, ld, (const bf16*)kpool,
+                         (const bf16*)vpool, tiles, cu_q, seg_pos0, block_table, bt_stride, page_size, (bf16*)out,
+                         Hq, Hkv, scale * LOG2E, window, sink, sm);
+}
+
 RB_EXPORT int rb_attn_prefill(const void* q, int ld, const void* kpool, const void* vpool, const int* tiles,
                               int n_tiles, const int* cu_q, const int* seg_pos0, const int* block_table,
                               int bt_stride, int page_size, void* out, int Hq, int Hkv, float scale,
                               int window, const float* sink, cudaStream_t st) {
-    if (n_tiles <= 0) return 0;
-    const size_t smem = (size_t)(PF_M + 4 * PF_N) * D * sizeof(bf16) + BT_CAP * sizeof(int);
-    static PerDevice configured;
-    const int cfg = configured.once([&](int) {
-        return cudaFuncSetAttribute(attn_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    });
-    if (cfg != 0) return cfg;
-    dim3 grid(n_tiles, Hq);
-    return rb_launch_pdl(attn_prefill_kernel, grid, dim3(128), smem, st, (const bf16*)q, ld, (const bf16*)kpool,
-                         (const bf16*)vpool, tiles, cu_q, seg_pos0, block_table, bt_stride, page_size, (bf16*)out,
-                         Hq, Hkv, scale * LOG2E, window, sink);
+    return rb_attn_prefill_mod(q, ld, kpool, vpool, tiles, n_tiles, cu_q, seg_pos0, block_table, bt_stride, page_size, out,
+                               Hq, Hkv, scale, window, sink, 0, 0.f, nullptr, st);
 }
 
 // Floats of scratch that rb_attn_decode needs: part_o [n_dec, Hq, splits, D], part_ml [n_dec, Hq, splits, 2].
@@ -779,7 +837,8 @@ namespace {
 int launch_decode(const void* q, int ld, const void* kpool, const void* vpool, const int* dec_segs,
                   int n_dec, const int* cu_q, const int* seg_kv_len, const int* block_table,
                   int bt_stride, int page_size, float* scratch, void* out, int Hq, int Hkv,
-                  float scale, int window, int num_splits, const FusedRope* fused, const float* sink, cudaStream_t st) {
+                  float scale, int window, int num_splits, const FusedRope* fused, const float* sink, cudaStream_t st,
+                  const ScoreMod* mod = nullptr) {
     if (n_dec <= 0) return 0;
     if (num_splits < 1 || num_splits > COMBINE_MAX_SPLITS || (num_splits > 1 && scratch == nullptr)) return (int)cudaErrorInvalidValue;
     const int G = Hq / Hkv, m_tiles = (G + 15) / 16;
@@ -789,8 +848,9 @@ int launch_decode(const void* q, int ld, const void* kpool, const void* vpool, c
     // the kernels' shared-memory limit is a setting per device: made once for each device that calls
     static PerDevice configured;
     const int cfg = configured.once([&](int) {
-        cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e == cudaSuccess) e = cudaFuncSetAttribute(attn_decode_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(attn_decode_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(attn_decode_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         return e;
     });
     if (cfg != 0) return cfg;
@@ -798,15 +858,21 @@ int launch_decode(const void* q, int ld, const void* kpool, const void* vpool, c
     float* part_ml = scratch ? scratch + (size_t)n_dec * Hq * num_splits * D : nullptr;
     dim3 grid(n_dec, Hkv * m_tiles, num_splits);
     FusedRope none = {};
+    ScoreMod plain = {};
     int rc;
-    if (fused != nullptr)
-        rc = rb_launch_pdl(attn_decode_kernel<true>, grid, dim3(DC_WARPS * 32), smem, st,
+    if (mod != nullptr && fused != nullptr) return (int)cudaErrorInvalidValue;
+    if (mod != nullptr)
+        rc = rb_launch_pdl(attn_decode_kernel<false, true>, grid, dim3(DC_WARPS * 32), smem, st,
             (const bf16*)q, ld, (const bf16*)kpool, (const bf16*)vpool, dec_segs, cu_q, seg_kv_len, block_table,
-            bt_stride, page_size, part_o, part_ml, (bf16*)out, Hq, Hkv, m_tiles, scale * LOG2E, window, num_splits, *fused, sink);
+            bt_stride, page_size, part_o, part_ml, (bf16*)out, Hq, Hkv, m_tiles, scale * LOG2E, window, num_splits, none, sink, *mod);
+    else if (fused != nullptr)
+        rc = rb_launch_pdl(attn_decode_kernel<true, false>, grid, dim3(DC_WARPS * 32), smem, st,
+            (const bf16*)q, ld, (const bf16*)kpool, (const bf16*)vpool, dec_segs, cu_q, seg_kv_len, block_table,
+            bt_stride, page_size, part_o, part_ml, (bf16*)out, Hq, Hkv, m_tiles, scale * LOG2E, window, num_splits, *fused, sink, plain);
     else
-        rc = rb_launch_pdl(attn_decode_kernel<false>, grid, dim3(DC_WARPS * 32), smem, st,
+        rc = rb_launch_pdl(attn_decode_kernel<false, false>, grid, dim3(DC_WARPS * 32), smem, st,
             (const bf16*)q, ld, (const bf16*)kpool, (const bf16*)vpool, dec_segs, cu_q, seg_kv_len, block_table,
-            bt_stride, page_size, part_o, part_ml, (bf16*)out, Hq, Hkv, m_tiles, scale * LOG2E, window, num_splits, none, sink);
+            bt_stride, page_size, part_o, part_ml, (bf16*)out, Hq, Hkv, m_tiles, scale * LOG2E, window, num_splits, none, sink, plain);
     if (rc != 0 || num_splits == 1) return rc;
     dim3 cgrid(n_dec, Hq);
     return rb_launch_pdl(attn_combine_kernel, cgrid, dim3(128), 0, st, (const float*)part_o, (const float*)part_ml,
@@ -820,6 +886,22 @@ RB_EXPORT int rb_attn_decode(const void* q, int ld, const void* kpool, const voi
                              float scale, int window, int num_splits, const float* sink, cudaStream_t st) {
     return launch_decode(q, ld, kpool, vpool, dec_segs, n_dec, cu_q, seg_kv_len, block_table, bt_stride, page_size,
                          scratch, out, Hq, Hkv, scale, window, num_splits, nullptr, sink, st);
+}
+
+// The split-KV kernel with the score options of rb_attn_prefill_mod.
+RB_EXPORT int rb_attn_decode_mod(const void* q, int ld, const void* kpool, const void* vpool, const int* dec_segs,
+                                 int n_dec, const int* cu_q, const int* seg_kv_len, const int* block_table,
+                                 int bt_stride, int page_size, float* scratch, void* out, int Hq, int Hkv,
+                                 float scale, int window, int num_splits, const float* sink, int chunk, float softcap,
+                                 const float* slopes, cudaStream_t st) {
+    if (window > 0 && chunk > 0) return (int)cudaErrorInvalidValue;
+    if (chunk <= 0 && softcap <= 0.f && slopes == nullptr)
+        return launch_decode(q, ld, kpool, vpool, dec_segs, n_dec, cu_q, seg_kv_len, block_table, bt_stride, page_size,
+                             scratch, out, Hq, Hkv, scale, window, num_splits, nullptr, sink, st);
+    ScoreMod sm;
+    sm.scale = scale; sm.softcap = softcap; sm.slopes = slopes; sm.chunk = chunk;
+    return launch_decode(q, ld, kpool, vpool, dec_segs, n_dec, cu_q, seg_kv_len, block_table, bt_stride, page_size,
+                         scratch, out, Hq, Hkv, scale, window, num_splits, nullptr, sink, st, &sm);
 }
 
 // The same for a step of single tokens only, with the q/k norm, the rotation and the cache write of

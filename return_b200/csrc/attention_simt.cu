@@ -11,6 +11,11 @@
 // q: rotated queries inside the QKV buffer, row stride ld.  K and V: one layer's pools
 // [num_pages, Hkv, P, D].  A key at position j is visible to the query at position p iff
 // lo <= j <= p with lo = max(0, p - window + 1) when window > 0, else 0.
+//
+// Options of the score, all off by default: `chunk` > 0 bounds the keys from below by the start of the query's own
+// block of `chunk` positions (blocks counted from position 0) instead of a window; `softcap` > 0 turns a scaled score
+// s into softcap * tanh(s / softcap); `slopes` [Hq] takes slopes[h] * (p - j) off the score of key j; `sink` [Hq] adds
+// exp(sink[h]) to the softmax's denominator (a term with no key and no value).
 #include "common.cuh"
 
 #define SIMT_MAX_D 256
@@ -21,7 +26,8 @@ attention_simt_kernel(const TA* __restrict__ q, int ld, const TA* __restrict__ k
                       const TA* __restrict__ vpool, const int* __restrict__ pos,
                       const int* __restrict__ tok_seg, const int* __restrict__ block_table,
                       int bt_stride, int page_size, TA* __restrict__ out, int Hq, int Hkv, int D,
-                      float scale, int window) {
+                      float scale, int window, int chunk, float softcap, const float* __restrict__ slopes,
+                      const float* __restrict__ sink) {
     extern __shared__ float qs_all[];                    // 4 warps x D floats
     const int t = blockIdx.x;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -30,7 +36,8 @@ attention_simt_kernel(const TA* __restrict__ q, int ld, const TA* __restrict__ k
     const int G = Hq / Hkv, kvh = h / G;
     const int p = pos[t];
     const int* bt = block_table + (size_t)tok_seg[t] * bt_stride;
-    const int lo = window > 0 ? max(0, p - window + 1) : 0;
+    const int lo = window > 0 ? max(0, p - window + 1) : chunk > 0 ? (p / chunk) * chunk : 0;
+    const float slope = slopes ? slopes[h] : 0.f;
     float* qs = qs_all + warp * D;
     const TA* qrow = q + (size_t)t * ld + (size_t)h * D;
     for (int d = lane; d < D; d += 32) qs[d] = to_f32(qrow[d]);
@@ -55,6 +62,8 @@ attention_simt_kernel(const TA* __restrict__ q, int ld, const TA* __restrict__ k
                 float dot = 0.f;
                 for (int d = 0; d < D; ++d) dot = fmaf(qs[d], to_f32(kr[d]), dot);
                 s = dot * scale;
+                if (softcap > 0.f) s = softcap * tanhf(s / softcap);
+                if (slopes) s -= slope * (float)(p - j);
             }
         }
         const float m_new = fmaxf(m, warp_max(s));
@@ -79,6 +88,7 @@ attention_simt_kernel(const TA* __restrict__ q, int ld, const TA* __restrict__ k
         m = m_new;
     }
     TA* orow = out + ((size_t)t * Hq + h) * D;
+    if (sink) l += expf(sink[h] - m);
     const float inv = 1.0f / l;
 #pragma unroll
     for (int i = 0; i < SIMT_MAX_D / 32; ++i) {
@@ -87,21 +97,31 @@ attention_simt_kernel(const TA* __restrict__ q, int ld, const TA* __restrict__ k
     }
 }
 
-RB_EXPORT int rb_attention_simt(const void* q, int ld, const void* kpool, const void* vpool,
+RB_EXPORT int rb_attention_simt_mod(const void* q, int ld, const void* kpool, const void* vpool,
                                 const int* pos, const int* tok_seg, const int* block_table,
                                 int bt_stride, int page_size, void* out, int act_dtype, int T,
-                                int Hq, int Hkv, int D, float scale, int window, cudaStream_t st) {
+                                int Hq, int Hkv, int D, float scale, int window, int chunk, float softcap,
+                                const float* slopes, const float* sink, cudaStream_t st) {
     if (T <= 0) return 0;
+    if (window > 0 && chunk > 0) return (int)cudaErrorInvalidValue;
     if (D > SIMT_MAX_D || D <= 0 || Hkv <= 0 || Hq % Hkv) return (int)cudaErrorInvalidValue;
     dim3 grid(T, (Hq + 3) / 4);
     const size_t smem = (size_t)4 * D * sizeof(float);
     if (act_dtype == RB_F32)
         attention_simt_kernel<float><<<grid, 128, smem, st>>>(
             (const float*)q, ld, (const float*)kpool, (const float*)vpool, pos, tok_seg, block_table,
-            bt_stride, page_size, (float*)out, Hq, Hkv, D, scale, window);
+            bt_stride, page_size, (float*)out, Hq, Hkv, D, scale, window, chunk, softcap, slopes, sink);
     else
         attention_simt_kernel<bf16><<<grid, 128, smem, st>>>(
             (const bf16*)q, ld, (const bf16*)kpool, (const bf16*)vpool, pos, tok_seg, block_table,
-            bt_stride, page_size, (bf16*)out, Hq, Hkv, D, scale, window);
+            bt_stride, page_size, (bf16*)out, Hq, Hkv, D, scale, window, chunk, softcap, slopes, sink);
     return rb_launch_status();
+}
+
+RB_EXPORT int rb_attention_simt(const void* q, int ld, const void* kpool, const void* vpool,
+                                const int* pos, const int* tok_seg, const int* block_table,
+                                int bt_stride, int page_size, void* out, int act_dtype, int T,
+                                int Hq, int Hkv, int D, float scale, int window, cudaStream_t st) {
+    return rb_attention_simt_mod(q, ld, kpool, vpool, pos, tok_seg, block_table, bt_stride, page_size, out, act_dtype, T,
+                                 Hq, Hkv, D, scale, window, 0, 0.f, nullptr, nullptr, st);
 }

@@ -22,7 +22,8 @@ __device__ __forceinline__ void warp_argmax(float& v, int& i) {
 
 __global__ void __launch_bounds__(128)
 moe_route_kernel(const float* __restrict__ z, int ldz, const float* __restrict__ bias, int* __restrict__ expert_of,
-                 float* __restrict__ weight, int T, int E, int top, int groups, int keep, float tiny) {
+                 float* __restrict__ weight, int T, int E, int top, int groups, int keep, float tiny, int score_fn,
+                 int group_top, float out_scale) {
     extern __shared__ float route_smem[];                 // per warp: E scores, then `groups` group scores
     pdl_launch_dependents();
     pdl_wait();
@@ -32,29 +33,36 @@ moe_route_kernel(const float* __restrict__ z, int ldz, const float* __restrict__
     float* s = route_smem + (size_t)warp * (E + groups);
     float* gs = s + E;
     const float* zr = z + (size_t)t * ldz;
-    float m = -INFINITY;
-    for (int e = lane; e < E; e += 32) {
-        const float v = zr[e] + (bias ? bias[e] : 0.f);    // the logit with its bias waits in s[e] for the second pass
-        s[e] = v;
-        m = fmaxf(m, v);
+    if (score_fn == 1) {                                  // every expert scored by itself: the logistic of its logit
+        for (int e = lane; e < E; e += 32) s[e] = 1.0f / (1.0f + expf(-(zr[e] + (bias ? bias[e] : 0.f))));
+    } else {
+        float m = -INFINITY;
+        for (int e = lane; e < E; e += 32) {
+            const float v = zr[e] + (bias ? bias[e] : 0.f);    // the logit with its bias waits in s[e] for the second pass
+            s[e] = v;
+            m = fmaxf(m, v);
+        }
+        m = warp_max(m);
+        float sum = 0.f;
+        for (int e = lane; e < E; e += 32) {
+            const float v = expf(s[e] - m);
+            s[e] = v;
+            sum += v;
+        }
+        sum = warp_sum(sum);
+        const float inv = 1.0f / sum;
+        for (int e = lane; e < E; e += 32) s[e] *= inv;
     }
-    m = warp_max(m);
-    float sum = 0.f;
-    for (int e = lane; e < E; e += 32) {
-        const float v = expf(s[e] - m);
-        s[e] = v;
-        sum += v;
-    }
-    sum = warp_sum(sum);
-    const float inv = 1.0f / sum;
-    for (int e = lane; e < E; e += 32) s[e] *= inv;
     __syncwarp();
     const int gsize = E / groups;
     if (groups > 1) {
         for (int g = lane; g < groups; g += 32) {
-            float b = -1.f;
-            for (int e = g * gsize; e < (g + 1) * gsize; ++e) b = fmaxf(b, s[e]);
-            gs[g] = b;
+            float b = -1.f, b2 = -1.f;                        // the group's two best scores
+            for (int e = g * gsize; e < (g + 1) * gsize; ++e) {
+                const float v = s[e];
+                if (v > b) { b2 = b; b = v; } else if (v > b2) { b2 = v; }
+            }
+            gs[g] = (group_top >= 2 && b2 >= 0.f) ? b + b2 : b;
         }
         __syncwarp();
         for (int r = 0; r < keep; ++r) {                  // the best group not yet kept becomes -2: kept
@@ -86,20 +94,21 @@ moe_route_kernel(const float* __restrict__ z, int ldz, const float* __restrict__
         total += bv;
         __syncwarp();
     }
-    const float scale = 1.0f / (total + tiny);
+    const float scale = out_scale / (total + tiny);
     __syncwarp();
     for (int k = lane; k < top; k += 32) weight[(size_t)t * top + k] *= scale;
 }
 
 RB_EXPORT int rb_moe_route(const float* z, int ldz, const float* bias, int* expert_of, float* weight, int T, int E, int top,
-                           int groups, int keep, float tiny, cudaStream_t st) {
+                           int groups, int keep, float tiny, int score_fn, int group_top, float out_scale, cudaStream_t st) {
     if (T <= 0) return 0;
+    if (score_fn < 0 || score_fn > 1 || group_top < 1 || group_top > 2) return (int)cudaErrorInvalidValue;
     if (groups < 1 || E % groups || top < 1 || top > E || keep < 1 || keep > groups || (long long)keep * (E / groups) < top)
         return (int)cudaErrorInvalidValue;
     const size_t smem = (size_t)4 * (E + groups) * sizeof(float);
     if (smem > 48 * 1024) return (int)cudaErrorInvalidValue;
     return rb_launch_pdl(moe_route_kernel, dim3((T + 3) / 4), dim3(128), smem, st, z, ldz, bias, expert_of, weight, T, E, top,
-                         groups, keep, tiny);
+                         groups, keep, tiny, score_fn, group_top, out_scale);
 }
 
 // ---------------------------------------------------------------- a pair's product, weights streamed

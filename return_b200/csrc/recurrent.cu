@@ -5,6 +5,7 @@
 // A head's state S is a [D, V] matrix in float32 that is read out as o = S^T q.  One token's update is
 //     fixed decay:     S <- a S + k v^T                                   o = S^T q
 //     delta rule:      S <- g * S (row i by g_i);  u = beta (v - S^T k);  S <- S + k u^T;  o = S^T q
+//     delta rule, one decay a head: the same with a scalar g per token and head
 //     matrix memory:   m' = max(f + m, i);  a = exp(f + m - m'),  b = exp(i - m');
 //                      S <- a S + b k v^T;  n <- a n + b k;  o = S^T q / (max(|n . q|, exp(-m')) + 1e-6)
 //     bonus rule:      o = (S + diag(u) k v^T)^T q;  S <- g * S (row i by g_i) + k v^T: the token's own pair is read with
@@ -35,6 +36,7 @@
 #define MODE_DELTA 2
 #define MODE_BONUS 3
 #define MODE_SSM 4
+#define MODE_DELTA_HEAD 5
 
 struct ScanArgs {
     const void* q; const void* k; const void* v;        // (t, head, i) at base + t * ld + head * dim + i
@@ -43,6 +45,7 @@ struct ScanArgs {
     const float* gate_a;      // decay: [H] decays; memory: [T, 2H] gate pre-activations (input, forget); delta and bonus:
                               // [T, H*D] row decays; state space: [T, H] decays
     const float* gate_b;      // memory: [2H] gate biases; delta: [T, H] beta; state space: [T, H] steps
+                              // delta with one decay a head: gate_a [T, H] decays, gate_b [T, H] beta
     const float* extra;       // bonus: [H, D] weights of the token's own pair; state space: [H] skip weights
     float cap, q_scale;
     float* state;             // [slots, state_stride]
@@ -157,7 +160,7 @@ linear_scan_kernel(const ScanArgs a) {
                 rb = a.gate_a[t * 2 * H + H + h];
             } else if (MODE == MODE_DELTA) {
                 rb = a.gate_b[t * H + h];
-            } else if (MODE == MODE_SSM) {
+            } else if (MODE == MODE_SSM || MODE == MODE_DELTA_HEAD) {
                 ra = a.gate_a[t * H + h];
                 rb = a.gate_b[t * H + h];
             }
@@ -238,10 +241,16 @@ linear_scan_kernel(const ScanArgs a) {
                 o4[ii & 3] = fmaf(S[ii], qr[ii], o4[ii & 3]);
             }
         } else {
+            if (MODE == MODE_DELTA_HEAD) {
+                const float g1 = sa[tt];
 #pragma unroll
-            for (int i4 = 0; i4 < NR; i4 += 4) {
-                const float4 g4 = *(const float4*)&sg[tt][r * RS + i4];
-                S[i4] *= g4.x; S[i4 + 1] *= g4.y; S[i4 + 2] *= g4.z; S[i4 + 3] *= g4.w;
+                for (int ii = 0; ii < NR; ++ii) S[ii] *= g1;
+            } else {
+#pragma unroll
+                for (int i4 = 0; i4 < NR; i4 += 4) {
+                    const float4 g4 = *(const float4*)&sg[tt][r * RS + i4];
+                    S[i4] *= g4.x; S[i4 + 1] *= g4.y; S[i4 + 2] *= g4.z; S[i4 + 3] *= g4.w;
+                }
             }
             float k4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
@@ -345,6 +354,7 @@ RB_EXPORT int rb_linear_scan(int mode, const void* q, const void* k, const void*
     if (mode == MODE_DELTA) return launch_scan<MODE_DELTA>(a, segments, st);
     if (mode == MODE_BONUS) return extra ? launch_scan<MODE_BONUS>(a, segments, st) : (int)cudaErrorInvalidValue;
     if (mode == MODE_SSM) return extra && gate_b ? launch_scan<MODE_SSM>(a, segments, st) : (int)cudaErrorInvalidValue;
+    if (mode == MODE_DELTA_HEAD) return gate_b ? launch_scan<MODE_DELTA_HEAD>(a, segments, st) : (int)cudaErrorInvalidValue;
     return (int)cudaErrorInvalidValue;
 }
 
@@ -585,7 +595,8 @@ RB_EXPORT int rb_rotary_inplace(void* x, int ld, const float* cos_t, const float
 //   token's; what lies before the segment comes from the request's conv state, which holds the K - 1 inputs
 //   before it, oldest first, and is zero for a new request), then silu; q and k heads are then made unit
 //   vectors (x / sqrt(sum x^2 + 1e-6)), q also times q_scale.  Channels: q heads, k heads, v heads, in this order.
-//   decay[t, h, i] = exp(-exp(A_log[h]) * softplus(a[t, h, i] + dt_bias[h, i]))   (in place over a)
+//   decay[t, h, i] = exp(-exp(A_log[h]) * softplus(a[t, h, i] + dt_bias[h, i]))   (in place over a; i < DA, which is D
+//   for a decay per key row and 1 for one decay a head)
 //   beta[t, h] = sigmoid(b[t, h])                                                 (in place over b)
 template <typename TA>
 __global__ void __launch_bounds__(128)
@@ -594,7 +605,7 @@ delta_prep_kernel(const TA* __restrict__ x, int ld, const void* __restrict__ tap
                   const int* __restrict__ tok_seg, const int* __restrict__ cu_q, const int* __restrict__ seg_slot,
                   float* __restrict__ q32, float* __restrict__ k32, float* __restrict__ v32,
                   float* __restrict__ a, const void* __restrict__ A_log, const void* __restrict__ dt_bias, int vec_dtype,
-                  float* __restrict__ b, int H, int G, int D, int V, float q_scale) {
+                  float* __restrict__ b, int H, int G, int D, int V, float q_scale, int DA) {
     __shared__ float scratch[33];
     pdl_wait();
     const int t = blockIdx.x, unit = blockIdx.y;
@@ -602,9 +613,9 @@ delta_prep_kernel(const TA* __restrict__ x, int ld, const void* __restrict__ tap
         if (unit < 2 * G + 2 * H) {
             const int h = unit - 2 * G - H;
             const float rate = expf(load_as_f32(A_log, vec_dtype, h));
-            for (int i = threadIdx.x; i < D; i += blockDim.x) {
-                const size_t e = ((size_t)t * H + h) * D + i;
-                a[e] = expf(-rate * softplus_f(a[e] + load_as_f32(dt_bias, vec_dtype, (size_t)h * D + i)));
+            for (int i = threadIdx.x; i < DA; i += blockDim.x) {
+                const size_t e = ((size_t)t * H + h) * DA + i;
+                a[e] = expf(-rate * softplus_f(a[e] + load_as_f32(dt_bias, vec_dtype, (size_t)h * DA + i)));
             }
         } else {
             for (int h = threadIdx.x; h < H; h += blockDim.x) b[(size_t)t * H + h] = sigmoid_f(b[(size_t)t * H + h]);
@@ -643,16 +654,17 @@ RB_EXPORT int rb_delta_prep(const void* x, int ld, const void* taps, int taps_dt
                             long long state_stride, int conv_off, const int* tok_seg, const int* cu_q, const int* seg_slot,
                             float* q32, float* k32, float* v32, float* a, const void* A_log, const void* dt_bias,
                             int vec_dtype, float* b, int act_dtype, int T, int H, int G, int D, int V, float q_scale,
-                            cudaStream_t st) {
+                            int head_decay, cudaStream_t st) {
     if (T <= 0) return 0;
     if (K < 1) return (int)cudaErrorInvalidValue;
+    const int DA = head_decay ? 1 : D;
     dim3 grid(T, 2 * G + 2 * H + 1);
     if (act_dtype == RB_F32)
         rb_launch_pdl(delta_prep_kernel<float>, dim3(grid), dim3(128), 0, st, (const float*)x, ld, taps, taps_dtype, K, state, state_stride, conv_off,
-            tok_seg, cu_q, seg_slot, q32, k32, v32, a, A_log, dt_bias, vec_dtype, b, H, G, D, V, q_scale);
+            tok_seg, cu_q, seg_slot, q32, k32, v32, a, A_log, dt_bias, vec_dtype, b, H, G, D, V, q_scale, DA);
     else
         rb_launch_pdl(delta_prep_kernel<bf16>, dim3(grid), dim3(128), 0, st, (const bf16*)x, ld, taps, taps_dtype, K, state, state_stride, conv_off,
-            tok_seg, cu_q, seg_slot, q32, k32, v32, a, A_log, dt_bias, vec_dtype, b, H, G, D, V, q_scale);
+            tok_seg, cu_q, seg_slot, q32, k32, v32, a, A_log, dt_bias, vec_dtype, b, H, G, D, V, q_scale, DA);
     return rb_launch_status();
 }
 
@@ -995,4 +1007,110 @@ RB_EXPORT int rb_gated_part_norm(const float* y, const void* z, int z_ld, const 
                              (float*)out, rows, parts, size);
     return rb_launch_pdl(gated_part_norm_kernel<bf16>, dim3(blocks), dim3(128), 0, st, y, (const bf16*)z, z_ld, w, w_dtype, eps,
                          (bf16*)out, rows, parts, size);
+}
+
+// ---------------------------------------------------------------- gated linear recurrence per channel
+// A recurrent branch of `W` channels beside a gate branch:  u = conv(x + x_bias) + conv_bias (a causal convolution
+// over time per channel, taps [W, K] with the last column for the token itself; what lies before position 0 is zero,
+// what lies before the step comes from the request's held inputs, which are kept without the bias);  with gate
+// pre-activations r~, i~ (block-diagonal maps of u, computed outside; float32 [2][blocks][T][block size]):  r = sigmoid(r~ + rb), i = sigmoid(i~ + ib),
+// log f = -c r softplus(lam), s <- f s + sqrt(1 - f^2) i u, out = s * gelu_tanh(y + y_bias).  Everything from the
+// gates on is float32; the state s [W] of a request lives in its slot and starts at zero.
+template <typename TA>
+__global__ void __launch_bounds__(128)
+gated_conv_kernel(const TA* __restrict__ x, int ld, const void* __restrict__ x_bias, const void* __restrict__ taps,
+                  const void* __restrict__ conv_bias, int w_dtype, int K, const float* __restrict__ state,
+                  long long state_stride, int conv_off, const int* __restrict__ pos, const int* __restrict__ tok_seg,
+                  const int* __restrict__ cu_q, const int* __restrict__ seg_slot, TA* __restrict__ u, int W) {
+    pdl_wait();
+    const int t = blockIdx.x;
+    const int c = blockIdx.y * blockDim.x + threadIdx.x;
+    if (c >= W) return;
+    const int seg = tok_seg[t];
+    const int l = t - cu_q[seg], p = pos[t];
+    const float* cs = state + (long long)seg_slot[seg] * state_stride + conv_off + (size_t)c * (K - 1);
+    const float xb = x_bias ? load_as_f32(x_bias, w_dtype, c) : 0.f;
+    float y = conv_bias ? load_as_f32(conv_bias, w_dtype, c) : 0.f;
+    for (int jb = K - 1; jb >= 0; --jb) {                  // jb tokens back, oldest first
+        if (jb > p) continue;                              // before the sequence: nothing
+        const float w = load_as_f32(taps, w_dtype, (size_t)c * K + (K - 1 - jb));
+        const float xv = jb <= l ? to_f32(x[(size_t)(t - jb) * ld + c]) : cs[K - 1 - (jb - l)];
+        y = fmaf(w, xv + xb, y);
+    }
+    u[(size_t)t * W + c] = from_f32<TA>(y);
+}
+
+RB_EXPORT int rb_gated_conv(const void* x, int ld, const void* x_bias, const void* taps, const void* conv_bias, int w_dtype,
+                            int K, const float* state, long long state_stride, int conv_off, const int* pos,
+                            const int* tok_seg, const int* cu_q, const int* seg_slot, void* u, int act_dtype, int T, int W,
+                            cudaStream_t st) {
+    if (T <= 0) return 0;
+    if (K < 1) return (int)cudaErrorInvalidValue;
+    dim3 grid(T, (W + 127) / 128);
+    if (act_dtype == RB_F32)
+        return rb_launch_pdl(gated_conv_kernel<float>, grid, dim3(128), 0, st, (const float*)x, ld, x_bias, taps, conv_bias, w_dtype, K,
+                             state, state_stride, conv_off, pos, tok_seg, cu_q, seg_slot, (float*)u, W);
+    return rb_launch_pdl(gated_conv_kernel<bf16>, grid, dim3(128), 0, st, (const bf16*)x, ld, x_bias, taps, conv_bias, w_dtype, K,
+                         state, state_stride, conv_off, pos, tok_seg, cu_q, seg_slot, (bf16*)u, W);
+}
+
+// One thread a channel walks its segment's tokens in order; the loads of RU tokens are issued before the first is used.
+#define GLR_UNROLL 8
+template <typename TA>
+__global__ void __launch_bounds__(128)
+gated_recurrence_kernel(const TA* __restrict__ u, const float* __restrict__ gates, int bs, const void* __restrict__ r_bias,
+                        const void* __restrict__ i_bias, const void* __restrict__ lam, int w_dtype, float c_decay,
+                        const TA* __restrict__ y, int y_ld, const void* __restrict__ y_bias, float* __restrict__ state,
+                        long long state_stride, int s_off, const int* __restrict__ cu_q, const int* __restrict__ seg_slot,
+                        TA* __restrict__ out, int W, int T) {
+    pdl_wait();
+    const int seg = blockIdx.y;
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= W) return;
+    const int t0 = cu_q[seg], t1 = cu_q[seg + 1];
+    float* sp = state + (long long)seg_slot[seg] * state_stride + s_off + c;
+    float s = *sp;
+    const int blk = c / bs, o = c - blk * bs;
+    const float* g_r = gates + (size_t)blk * T * bs + o;
+    const float* g_i = g_r + (size_t)W * T;
+    const float rb = load_as_f32(r_bias, w_dtype, c), ib = load_as_f32(i_bias, w_dtype, c);
+    const float sp_lam = softplus_f(load_as_f32(lam, w_dtype, c));
+    const float yb = y_bias ? load_as_f32(y_bias, w_dtype, c) : 0.f;
+    for (int tc = t0; tc < t1; tc += GLR_UNROLL) {
+        float ru[GLR_UNROLL], rr[GLR_UNROLL], ri[GLR_UNROLL], ry[GLR_UNROLL];
+#pragma unroll
+        for (int k = 0; k < GLR_UNROLL; ++k) {
+            const size_t t = (size_t)min(tc + k, t1 - 1);
+            ru[k] = to_f32(u[t * W + c]);
+            rr[k] = g_r[t * bs];
+            ri[k] = g_i[t * bs];
+            ry[k] = to_f32(y[t * y_ld + c]);
+        }
+#pragma unroll
+        for (int k = 0; k < GLR_UNROLL; ++k) {
+            if (tc + k < t1) {
+                const float r = sigmoid_f(rr[k] + rb), ig = sigmoid_f(ri[k] + ib);
+                const float lf = -c_decay * r * sp_lam;
+                const float f = expf(lf);
+                s = fmaf(f, s, sqrtf(-expm1f(2.f * lf)) * ig * ru[k]);
+                out[(size_t)(tc + k) * W + c] = from_f32<TA>(s * rb_activate(ACT_GELU_TANH, ry[k] + yb, nullptr, 0, 0));
+            }
+        }
+    }
+    *sp = s;
+}
+
+RB_EXPORT int rb_gated_recurrence(const void* u, const float* gates, int bs, const void* r_bias, const void* i_bias,
+                                  const void* lam, int w_dtype, float c_decay, const void* y, int y_ld, const void* y_bias,
+                                  float* state, long long state_stride, int s_off, const int* cu_q, const int* seg_slot,
+                                  void* out, int act_dtype, int W, int T, int segments, cudaStream_t st) {
+    if (segments <= 0) return 0;
+    if (bs <= 0 || W % bs) return (int)cudaErrorInvalidValue;
+    dim3 grid((W + 127) / 128, segments);
+    if (act_dtype == RB_F32)
+        return rb_launch_pdl(gated_recurrence_kernel<float>, grid, dim3(128), 0, st, (const float*)u, gates, bs, r_bias, i_bias, lam,
+                             w_dtype, c_decay, (const float*)y, y_ld, y_bias, state, state_stride, s_off, cu_q, seg_slot,
+                             (float*)out, W, T);
+    return rb_launch_pdl(gated_recurrence_kernel<bf16>, grid, dim3(128), 0, st, (const bf16*)u, gates, bs, r_bias, i_bias, lam,
+                         w_dtype, c_decay, (const bf16*)y, y_ld, y_bias, state, state_stride, s_off, cu_q, seg_slot, (bf16*)out, W, T);
 }

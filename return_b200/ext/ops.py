@@ -69,7 +69,8 @@ PDL_MODE = 2
 
 _core = None
 
-_CORE_SOURCES = ["elementwise.cu", "gemm_f32.cu", "gemm_skinny.cu", "rope_cache.cu", "attention_simt.cu", "sampling.cu"]
+_CORE_SOURCES = ["elementwise.cu", "gemm_f32.cu", "gemm_skinny.cu", "rope_cache.cu", "attention_simt.cu", "sampling.cu",
+                 "attention_prep.cu"]
 
 
 def core() -> ctypes.CDLL:
@@ -99,13 +100,19 @@ def core() -> ctypes.CDLL:
         lib.rb_gemm_skinny_ctas.restype = c_int
         lib.rb_qk_norm_rope_write.argtypes = [P, I, P, P, I, F, F, P, P, I, P, P, P, I, I, P, P, I, I, I, I, I, I, P]
         lib.rb_attention_simt.argtypes = [P, I, P, P, P, P, P, I, I, P, I, I, I, I, I, F, I, P]
+        lib.rb_attention_simt_mod.argtypes = [P, I, P, P, P, P, P, I, I, P, I, I, I, I, I, F, I, I, F, P, P, P]
+        lib.rb_attn_prep.argtypes = [P, I, I, I, I, P, P, P, I, P, P, I, F, P, P, I, P, P, P, I, I, P, P, P, I, I, I, I, I, I, I, I, P]
+        lib.rb_attn_gate.argtypes = [P, P, I, I, I, I, I, I, I, I, P]
+        lib.rb_embedding_pair.argtypes = [P, P, I, P, P, P, P, P, P, P, I, I, I, F, I, L, L, P]
+        lib.rb_last_token.argtypes = [P, P, P, P, I, P]
         lib.rb_sample.argtypes = [P, I, I, I, P, P, P, P, P, P, I, P]
         lib.rb_argmax.argtypes = [P, I, I, I, P, P]
         lib.rb_postnorm_add_norm.argtypes = [P, P, P, I, F, F, P, I, F, F, P, I, I, I, P]
         lib.rb_softcap.argtypes = [P, F, ctypes.c_longlong, P]
         for name in ("rb_embedding", "rb_add_rmsnorm", "rb_rmsnorm_rows", "rb_swiglu", "rb_gemm_f32",
                      "rb_qk_norm_rope_write", "rb_attention_simt", "rb_sample", "rb_argmax", "rb_postnorm_add_norm",
-                     "rb_softcap", "rb_activation", "rb_hyper_read_norm", "rb_hyper_write"):
+                     "rb_softcap", "rb_activation", "rb_hyper_read_norm", "rb_hyper_write", "rb_attention_simt_mod",
+                     "rb_attn_prep", "rb_attn_gate", "rb_embedding_pair", "rb_last_token"):
             getattr(lib, name).restype = c_int
         _core = lib
     return _core
@@ -141,6 +148,27 @@ def embedding(table: torch.Tensor, tokens: torch.Tensor, stream_out: torch.Tenso
     assert table.shape[1] == H and table.is_contiguous() and stream_out.is_contiguous()
     _check(core().rb_embedding(_ptr(table), dtype_code(table.dtype), _ptr(tokens), _ptr(stream_out),
                                T, H, table.shape[0], float(scale), copies, _stream()), "embedding")
+
+
+def embedding_pair(table, pairs, batch, last_token, stream_out, scale: float, buckets: int, mul_prev: int, mul_cur: int) -> None:
+    """stream_out[t] = scale * table[token] + pairs[row]: row = (previous token * mul_prev + token * mul_cur) mod buckets,
+    or row ``buckets`` for a sequence's first token.  The token before a segment's first one is ``last_token`` (int32, one
+    per state slot) of the segment's request; ``last_token_update`` renews it after the step."""
+    T, H = stream_out.shape
+    assert tuple(table.shape[1:]) == (H,) and tuple(pairs.shape) == (buckets + 1, H) and pairs.dtype == table.dtype
+    assert table.is_contiguous() and pairs.is_contiguous() and stream_out.is_contiguous() and stream_out.dtype == torch.float32
+    assert last_token.dtype == torch.int32 and batch.tokens.dtype == torch.int32
+    _check(core().rb_embedding_pair(_ptr(table), _ptr(pairs), dtype_code(table.dtype), _ptr(batch.tokens), _ptr(batch.pos),
+                                    _ptr(batch.tok_seg), _ptr(batch.cu_q), _ptr(batch.seg_slot), _ptr(last_token),
+                                    _ptr(stream_out), T, H, table.shape[0], scale, buckets, mul_prev, mul_cur, _stream()),
+           "embedding_pair")
+
+
+def last_token_update(batch, last_token) -> None:
+    """last_token[slot of a segment's request] = the segment's last token, for every segment of the step."""
+    assert last_token.dtype == torch.int32
+    _check(core().rb_last_token(_ptr(batch.tokens), _ptr(batch.cu_q), _ptr(batch.seg_slot), _ptr(last_token),
+                                batch.num_segments, _stream()), "last_token")
 
 
 ACTIVATIONS = {"relu2": 0, "tanh": 1, "gelu_tanh": 2, "silu": 3, "neg_exp_exp": 4}
@@ -604,6 +632,9 @@ def attention_lib(head_dim: int) -> ctypes.CDLL:
         lib.rb_attn_decode.argtypes = [P, I, P, P, P, I, P, P, P, I, I, P, P, I, I, F, I, I, P, P]
         lib.rb_attn_decode_fused.argtypes = [P, I, P, P, P, I, P, P, P, I, I, P, P, I, I, F, I, I, P, P, I, F, F, P, P, I, I, P]
         lib.rb_attn_decode_fused.restype = c_int
+        lib.rb_attn_prefill_mod.argtypes = [P, I, P, P, P, I, P, P, P, I, I, P, I, I, F, I, P, I, F, P, P]
+        lib.rb_attn_decode_mod.argtypes = [P, I, P, P, P, I, P, P, P, I, I, P, P, I, I, F, I, I, P, I, F, P, P]
+        lib.rb_attn_prefill_mod.restype = lib.rb_attn_decode_mod.restype = c_int
         lib.rb_attn_decode_scratch_floats.argtypes = [I, I, I]
         lib.rb_attn_decode_scratch_floats.restype = ctypes.c_longlong
         lib.rb_attn_prefill.restype = lib.rb_attn_decode.restype = lib.rb_attn_head_dim.restype = c_int
@@ -729,15 +760,17 @@ def decode_splits(n_ctas_base: int, max_kv_len: int, ctas_per_sm: int = 2) -> in
 
 
 def attention_prefill_mma(qkv, k_pool, v_pool, tiles, cu_q, seg_pos0, block_table, page_size, out, num_heads,
-                          num_kv_heads, head_dim, scale, window=0, sink=None) -> None:
-    """Tensor-core attention for the listed (segment, first row) tiles of up to 64 query rows."""
+                          num_kv_heads, head_dim, scale, window=0, sink=None, chunk=0, softcap=0.0, slopes=None) -> None:
+    """Tensor-core attention for the listed (segment, first row) tiles of up to 64 query rows.  ``chunk``, ``softcap``,
+    ``slopes``: the score options of ``paged_attention``."""
     assert qkv.dtype == torch.bfloat16 and k_pool.dtype == torch.bfloat16 and out.is_contiguous()
     assert tiles.dtype == torch.int32 and tiles.is_contiguous()
     lib = attention_lib(head_dim)
-    _check(lib.rb_attn_prefill(_ptr(qkv), qkv.stride(0), _ptr(k_pool), _ptr(v_pool), _ptr(tiles), tiles.shape[0],
-                               _ptr(cu_q), _ptr(seg_pos0), _ptr(block_table), block_table.stride(0), page_size,
-                               _ptr(out), num_heads, num_kv_heads, scale, int(window or 0), _sink_ptr(sink, num_heads),
-                               _stream()), "attention_prefill")
+    _check(lib.rb_attn_prefill_mod(_ptr(qkv), qkv.stride(0), _ptr(k_pool), _ptr(v_pool), _ptr(tiles), tiles.shape[0],
+                                   _ptr(cu_q), _ptr(seg_pos0), _ptr(block_table), block_table.stride(0), page_size,
+                                   _ptr(out), num_heads, num_kv_heads, scale, int(window or 0), _sink_ptr(sink, num_heads),
+                                   int(chunk or 0), float(softcap or 0.0), _sink_ptr(slopes, num_heads), _stream()),
+           "attention_prefill")
 
 
 def _split_scratch(lib, n, num_heads, num_splits, device, held=None):
@@ -754,16 +787,19 @@ def _split_scratch(lib, n, num_heads, num_splits, device, held=None):
 
 
 def attention_decode_mma(qkv, k_pool, v_pool, decode_segs, cu_q, seg_kv_len, block_table, page_size, out,
-                         num_heads, num_kv_heads, head_dim, scale, window=0, num_splits=1, held=None, sink=None) -> None:
-    """Tensor-core attention for segments of one token, the keys split ``num_splits`` ways."""
+                         num_heads, num_kv_heads, head_dim, scale, window=0, num_splits=1, held=None, sink=None,
+                         chunk=0, softcap=0.0, slopes=None) -> None:
+    """Tensor-core attention for segments of one token, the keys split ``num_splits`` ways.  ``chunk``, ``softcap``,
+    ``slopes``: the score options of ``paged_attention``."""
     assert qkv.dtype == torch.bfloat16 and k_pool.dtype == torch.bfloat16 and out.is_contiguous()
     lib = attention_lib(head_dim)
     n = decode_segs.shape[0]
     scratch = _split_scratch(lib, n, num_heads, num_splits, qkv.device, held)
-    _check(lib.rb_attn_decode(_ptr(qkv), qkv.stride(0), _ptr(k_pool), _ptr(v_pool), _ptr(decode_segs), n,
-                              _ptr(cu_q), _ptr(seg_kv_len), _ptr(block_table), block_table.stride(0), page_size,
-                              _ptr(scratch), _ptr(out), num_heads, num_kv_heads, scale, int(window or 0),
-                              num_splits, _sink_ptr(sink, num_heads), _stream()), "attention_decode", 2 if num_splits > 1 else 1)
+    _check(lib.rb_attn_decode_mod(_ptr(qkv), qkv.stride(0), _ptr(k_pool), _ptr(v_pool), _ptr(decode_segs), n,
+                                  _ptr(cu_q), _ptr(seg_kv_len), _ptr(block_table), block_table.stride(0), page_size,
+                                  _ptr(scratch), _ptr(out), num_heads, num_kv_heads, scale, int(window or 0),
+                                  num_splits, _sink_ptr(sink, num_heads), int(chunk or 0), float(softcap or 0.0),
+                                  _sink_ptr(slopes, num_heads), _stream()), "attention_decode", 2 if num_splits > 1 else 1)
 
 
 def _decode_split_count(batch, num_heads, num_kv_heads, window) -> int:
@@ -842,39 +878,87 @@ def attention_decode_fused(qkv, q_weight, k_weight, eps, offset, cos, sin, rot_d
 
 
 def paged_attention(qkv, k_pool, v_pool, batch, block_table, page_size, out, num_heads, num_kv_heads,
-                    head_dim, scale, window=None, sink=None) -> None:
+                    head_dim, scale, window=None, sink=None, chunk=None, softcap=None, slopes=None) -> None:
     """Attention of every token of the step over its request's cached keys (its own included).
 
     float32: the CUDA-core kernel, whose result does not depend on how the work was cut.
     bfloat16: the tensor-core kernels, one for prompt portions and one (split over the keys) for
-    single decoded tokens."""
+    single decoded tokens.
+
+    Options of the score: ``window`` (the last n keys) or ``chunk`` (the keys of the query's own block of n positions,
+    blocks counted from position 0), never both; ``sink`` (float32 [heads]: exp(sink) joins the softmax's denominator);
+    ``softcap`` (a scaled score s becomes cap * tanh(s / cap)); ``slopes`` (float32 [heads]: slopes[h] * (i - j) is taken
+    off the score of key j for query i).  Scores with a soft cap, slopes or a chunk run on the mma.sync kernels for every
+    head size (the tcgen05 prompt kernel has no such variant)."""
+    modded = bool(chunk) or bool(softcap) or slopes is not None
+    if window and chunk:
+        raise KernelError("a window and a chunk exclude each other")
     if qkv.dtype == torch.float32:
-        if sink is not None:
-            raise KernelError("the float32 attention kernel takes no sink")
-        attention_simt(qkv, k_pool, v_pool, batch.pos, batch.tok_seg, block_table, page_size, out,
-                       num_heads, num_kv_heads, head_dim, scale, window or 0)
+        T = qkv.shape[0]
+        assert out.is_contiguous() and out.dtype == qkv.dtype and k_pool.dtype == qkv.dtype
+        _check(core().rb_attention_simt_mod(
+            _ptr(qkv), qkv.stride(0), _ptr(k_pool), _ptr(v_pool), _ptr(batch.pos), _ptr(batch.tok_seg), _ptr(block_table),
+            block_table.stride(0), page_size, _ptr(out), dtype_code(qkv.dtype), T, num_heads, num_kv_heads, head_dim, scale,
+            int(window or 0), int(chunk or 0), float(softcap or 0.0), _sink_ptr(slopes, num_heads),
+            _sink_ptr(sink, num_heads), _stream()), "attention_simt")
         return
     host = batch.host
+    bound = window or chunk                       # either bounds the keys a query can see
     if host.num_multi:
-        if head_dim in TC5_ATTENTION_HEAD_DIMS:
+        if head_dim in TC5_ATTENTION_HEAD_DIMS and not modded:
             attention_prefill_tc5(qkv, k_pool, v_pool, batch.tiles[TILES_TC5], batch.cu_q, batch.seg_pos0, block_table,
                                   page_size, out, num_heads, num_kv_heads, head_dim, scale, window or 0,
                                   _prefill_split_count(batch, num_heads, window), getattr(batch, "scratch", None), sink)
         else:
             attention_prefill_mma(qkv, k_pool, v_pool, batch.tiles[TILES_MMA], batch.cu_q, batch.seg_pos0, block_table,
-                                  page_size, out, num_heads, num_kv_heads, head_dim, scale, window or 0, sink)
+                                  page_size, out, num_heads, num_kv_heads, head_dim, scale, window or 0, sink,
+                                  chunk, softcap, slopes)
     n_dec = host.decode_segs.shape[0]
     if n_dec:
         attention_decode_mma(qkv, k_pool, v_pool, batch.decode_segs, batch.cu_q, batch.seg_kv_len, block_table,
                              page_size, out, num_heads, num_kv_heads, head_dim, scale, window or 0,
-                             _decode_split_count(batch, num_heads, num_kv_heads, window), getattr(batch, "scratch", None), sink)
+                             _decode_split_count(batch, num_heads, num_kv_heads, bound), getattr(batch, "scratch", None), sink,
+                             chunk, softcap, slopes)
+
+
+def attention_prepare(proj, q_off: int, k_off: int, v_off: int, biases, norms, eps: float, tables, batch, kv, q_out,
+                      num_heads: int, num_kv_heads: int, dim: int, vdim: int, head_dim: int, write_kv: bool = True) -> None:
+    """From a step's projection rows to what the paged attention kernels read, for an attention that prepares a row as a
+    whole (csrc/attention_prep.cu).  ``proj`` [T, >= ...]: q heads of ``dim`` from column ``q_off``, k heads from ``k_off``,
+    v heads of ``vdim`` from ``v_off`` (``v_off`` < 0: the values are the key projection as it is).  ``biases``: None or
+    (q, k, v) added first; ``norms``: None or (q weight, k weight) of an RMS norm over the whole q and the whole k
+    projection; ``tables``: None or (cos, sin, rot) rotating elements (2i, 2i + 1), i < rot / 2, of every q and k head.
+    q goes to ``q_out`` [T, heads * head_dim], keys and values into the pages of ``kv`` (heads padded to ``head_dim``)."""
+    T = proj.shape[0]
+    assert proj.stride(1) == 1 and q_out.is_contiguous() and q_out.dtype == proj.dtype
+    assert tuple(q_out.shape) == (T, num_heads * head_dim) and kv.k.dtype == proj.dtype
+    qb, kb, vb = biases if biases is not None else (None, None, None)
+    qn, kn = norms if norms is not None else (None, None)
+    cos, sin, rot = tables if tables is not None else (batch.pos, batch.pos, 0)      # never read with a width of zero
+    if rot:
+        assert cos.dtype == sin.dtype == torch.float32 and cos.shape[1] * 2 == rot and cos.is_contiguous() and sin.is_contiguous()
+    _check(core().rb_attn_prep(
+        _ptr(proj), proj.stride(0), q_off, k_off, v_off, _ptr(qb), _ptr(kb), _ptr(vb),
+        dtype_code(qb.dtype) if qb is not None else F32, _ptr(qn), _ptr(kn), dtype_code(qn.dtype) if qn is not None else F32,
+        eps, _ptr(cos), _ptr(sin), rot, _ptr(batch.pos), _ptr(batch.tok_seg), _ptr(kv.block_table), kv.block_table.stride(0),
+        kv.page_size, _ptr(kv.k), _ptr(kv.v), _ptr(q_out), dtype_code(proj.dtype), T, num_heads, num_kv_heads, dim, vdim,
+        head_dim, 1 if write_kv else 0, _stream()), "attention_prepare")
+
+
+def attention_gate(o, gate, g_off: int, per_head: bool, num_heads: int, vdim: int, head_dim: int) -> None:
+    """o [T, heads * head_dim] in place: a head's first ``vdim`` elements times the logistic of their gate, taken from the
+    rows of ``gate`` from column ``g_off``: one gate a head (``per_head``) or one per value element."""
+    T = o.shape[0]
+    assert o.is_contiguous() and gate.stride(1) == 1 and gate.dtype == o.dtype and o.shape[1] == num_heads * head_dim
+    _check(core().rb_attn_gate(_ptr(o), _ptr(gate), gate.stride(0), g_off, 1 if per_head else 0, dtype_code(o.dtype), T,
+                               num_heads, vdim, head_dim, _stream()), "attention_gate")
 
 
 # ------------------------------------------------------------------------------- mixers with a matrix state
 
 _recurrent = None
 _RECURRENT_SOURCES = ["recurrent.cu"]
-SCAN_DECAY, SCAN_MEMORY, SCAN_DELTA, SCAN_BONUS, SCAN_SSM = 0, 1, 2, 3, 4
+SCAN_DECAY, SCAN_MEMORY, SCAN_DELTA, SCAN_BONUS, SCAN_SSM, SCAN_DELTA_HEAD = 0, 1, 2, 3, 4, 5
 SCAN_MAX_KEY_DIM = 256
 
 
@@ -898,7 +982,10 @@ def recurrent_lib() -> ctypes.CDLL:
         lib.rb_memory_pieces_combine.restype = c_int
         lib.rb_rotary_inplace.argtypes = [P, I, P, P, I, P, I, I, I, I, P]
         lib.rb_rotary_inplace.restype = c_int
-        lib.rb_delta_prep.argtypes = [P, I, P, I, I, P, L, I, P, P, P, P, P, P, P, P, P, I, P, I, I, I, I, I, I, F, P]
+        lib.rb_delta_prep.argtypes = [P, I, P, I, I, P, L, I, P, P, P, P, P, P, P, P, P, I, P, I, I, I, I, I, I, F, I, P]
+        lib.rb_gated_conv.argtypes = [P, I, P, P, P, I, I, P, L, I, P, P, P, P, P, I, I, I, P]
+        lib.rb_gated_recurrence.argtypes = [P, P, I, P, P, P, I, F, P, I, P, P, L, I, P, P, P, I, I, I, I, P]
+        lib.rb_gated_conv.restype = lib.rb_gated_recurrence.restype = c_int
         lib.rb_conv_state_update.argtypes = [P, I, I, P, L, I, P, P, I, I, I, P]
         lib.rb_head_norm_gate.argtypes = [P, P, I, P, I, I, I, F, P, I, I, I, I, P]
         lib.rb_add_dual_norm.argtypes = [P, P, I, F, P, I, F, P, P, P, I, F, F, P, P, I, I, I, P]
@@ -928,6 +1015,7 @@ def linear_scan(mode: int, q, k, v, gate_a, gate_b, state, offsets, batch, out, 
     matrix, the normaliser and the running maximum start inside a row (the last two for ``SCAN_MEMORY`` only).
     ``gate_a`` / ``gate_b`` by mode: SCAN_DECAY: [heads] decays / None; SCAN_MEMORY: [T, 2 heads] gate
     pre-activations (input, forget) / [2 heads] biases; SCAN_DELTA: [T, heads, dim] row decays / [T, heads] beta;
+    SCAN_DELTA_HEAD: [T, heads] decays / [T, heads] beta;
     SCAN_BONUS (o = (S + diag(u) k v^T)^T q, then S <- g * S + k v^T): [T, heads, dim] row decays / None, ``extra`` = u
     [heads, dim]; SCAN_SSM (S <- a S + dt k v^T, o = S^T q + d v): [T, heads] decays / [T, heads] steps, ``extra`` = d
     [heads].
@@ -1013,10 +1101,11 @@ def rotary_inplace(x, cos, sin, rot: int, pos, heads: int, dim: int) -> None:
 
 
 def delta_prep(x, taps, state, conv_off: int, batch, q32, k32, v32, a, A_log, dt_bias, b, heads: int, kv_heads: int,
-               dim: int, vdim: int, q_scale: float) -> None:
+               dim: int, vdim: int, q_scale: float, head_decay: bool = False) -> None:
     """What the delta rule needs of every token: the short causal convolution and silu of the q, k, v channels of
     ``x`` (what lies before a segment comes from the request's conv state), unit q and k heads, the row decays (in
-    place over ``a``) and beta (in place over ``b``)."""
+    place over ``a``) and beta (in place over ``b``).  ``head_decay``: ``a`` holds one number a token and head
+    ([T, heads], ``dt_bias`` [heads]) instead of one a key row."""
     T = x.shape[0]
     K = taps.shape[1]
     assert x.stride(1) == 1 and taps.is_contiguous() and taps.shape[0] == 2 * kv_heads * dim + heads * vdim
@@ -1028,7 +1117,39 @@ def delta_prep(x, taps, state, conv_off: int, batch, q32, k32, v32, a, A_log, dt
         _ptr(x), x.stride(0), _ptr(taps), dtype_code(taps.dtype), K, _ptr(state), state.stride(0), conv_off,
         _ptr(batch.tok_seg), _ptr(batch.cu_q), _ptr(batch.seg_slot), _ptr(q32), _ptr(k32), _ptr(v32), _ptr(a),
         _ptr(A_log), _ptr(dt_bias), dtype_code(A_log.dtype), _ptr(b), dtype_code(x.dtype), T, heads, kv_heads, dim, vdim,
-        q_scale, _stream()), "delta_prep")
+        q_scale, 1 if head_decay else 0, _stream()), "delta_prep")
+
+
+def gated_conv(x, x_bias, taps, conv_bias, state, conv_off: int, batch, out) -> None:
+    """out[t, c] = conv_bias[c] + sum_j taps[c, K - 1 - j] * (x[t - j, c] + x_bias[c]) over the tokens t - j at positions
+    >= 0 (what lies before the step comes from the request's held inputs: ``state`` row of its slot from ``conv_off``,
+    [channel][K - 1], kept without the bias).  x: a view [T, channels] with unit stride along a row; out [T, channels]."""
+    T, W = out.shape
+    K = taps.shape[1]
+    assert x.stride(1) == 1 and x.shape[1] >= W and out.is_contiguous() and out.dtype == x.dtype and taps.is_contiguous()
+    assert taps.shape[0] == W and state.dtype == torch.float32
+    for t in (x_bias, conv_bias):
+        assert t is None or (t.dtype == taps.dtype and t.numel() == W)
+    _check(recurrent_lib().rb_gated_conv(_ptr(x), x.stride(0), _ptr(x_bias), _ptr(taps), _ptr(conv_bias), dtype_code(taps.dtype),
+                                         K, _ptr(state), state.stride(0), conv_off, _ptr(batch.pos), _ptr(batch.tok_seg),
+                                         _ptr(batch.cu_q), _ptr(batch.seg_slot), _ptr(out), dtype_code(x.dtype), T, W, _stream()),
+           "gated_conv")
+
+
+def gated_recurrence(u, gates, block: int, r_bias, i_bias, lam, c_decay: float, y, y_bias, state, s_off: int, batch, out) -> None:
+    """Per channel c and segment, token by token: r = sigmoid(gates[0, b, t, o] + r_bias[c]), i = sigmoid(gates[1, b, t, o]
+    + i_bias[c]) with b = c // block, o = c % block (gates float32 [2, W / block, T, block]); log f = -c_decay r
+    softplus(lam[c]); s <- f s + sqrt(1 - f^2) i u[t, c]; out[t, c] = s * gelu_tanh(y[t, c] + y_bias[c]).  s is the float32
+    ``state`` row of the request's slot from ``s_off``."""
+    T, W = u.shape
+    assert u.is_contiguous() and out.is_contiguous() and out.shape == (T, W) and out.dtype == u.dtype == y.dtype
+    assert gates.dtype == torch.float32 and gates.is_contiguous() and gates.numel() == T * 2 * W and y.stride(1) == 1
+    assert r_bias.dtype == i_bias.dtype == lam.dtype and r_bias.numel() == i_bias.numel() == lam.numel() == W
+    assert y_bias is None or (y_bias.dtype == lam.dtype and y_bias.numel() == W)
+    _check(recurrent_lib().rb_gated_recurrence(_ptr(u), _ptr(gates), block, _ptr(r_bias), _ptr(i_bias), _ptr(lam),
+                                               dtype_code(lam.dtype), c_decay, _ptr(y), y.stride(0), _ptr(y_bias), _ptr(state),
+                                               state.stride(0), s_off, _ptr(batch.cu_q), _ptr(batch.seg_slot), _ptr(out),
+                                               dtype_code(u.dtype), W, T, batch.num_segments, _stream()), "gated_recurrence")
 
 
 def conv_state_update(x, taps_count: int, state, conv_off: int, batch, channels: int) -> None:
@@ -1095,10 +1216,11 @@ def head_norm_gate(o, gate, weight, weight_mode: int, gate_act: int, eps: float,
            "head_norm_gate")
 
 
-def add_dual_norm(stream, deltas, w1, w2, eps: float, offset: float, out1, out2, rows=None) -> None:
+def add_dual_norm(stream, deltas, w1, w2, eps: float, offset: float, out1, out2, rows=None, scales=(1.0, 1.0)) -> None:
     """stream (float32) += the deltas (up to two tensors of the stream's shape, float32 or bfloat16; written back
     unless ``rows``), then out1 = norm(stream) * (offset + w1) and, if given, out2 likewise with w2: two norms of the
-    same row share its mean square.  out1 None: the add only.  ``rows`` (int32): only these rows are normed."""
+    same row share its mean square.  out1 None: the add only.  ``rows`` (int32): only these rows are normed.
+    ``scales``: a factor on each delta as it is added."""
     H = stream.shape[1]
     assert stream.dtype == torch.float32 and stream.is_contiguous()
     ds = [d for d in (deltas or ()) if d is not None]
@@ -1115,8 +1237,8 @@ def add_dual_norm(stream, deltas, w1, w2, eps: float, offset: float, out1, out2,
     elif not ds:
         return
     _check(recurrent_lib().rb_add_dual_norm(
-        _ptr(stream), _ptr(d1), _is_f32(d1) if d1 is not None else 1, 1.0, _ptr(d2), _is_f32(d2) if d2 is not None else 1,
-        1.0, _ptr(rows), _ptr(w1), _ptr(w2), dtype_code(w1.dtype) if w1 is not None else F32, eps, offset, _ptr(out1),
+        _ptr(stream), _ptr(d1), _is_f32(d1) if d1 is not None else 1, float(scales[0]), _ptr(d2),
+        _is_f32(d2) if d2 is not None else 1, float(scales[1]), _ptr(rows), _ptr(w1), _ptr(w2), dtype_code(w1.dtype) if w1 is not None else F32, eps, offset, _ptr(out1),
         _ptr(out2), dtype_code(out1.dtype) if out1 is not None else F32, n, H, _stream()), "add_dual_norm")
 
 
@@ -1285,7 +1407,10 @@ def linear_heads(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
         return
     if not x.is_cuda:
         raise KernelError("the engine's kernels run on a CUDA device only; got a CPU tensor")
-    torch.bmm(x, w.transpose(1, 2), out=out)
+    if out.dtype == torch.float32:
+        torch.bmm(x, w.transpose(1, 2), out_dtype=torch.float32, out=out)
+    else:
+        torch.bmm(x, w.transpose(1, 2), out=out)
 
 
 # ------------------------------------------------------------------------------- mixture of experts
@@ -1300,7 +1425,7 @@ def moe_lib() -> ctypes.CDLL:
     if _moe is None:
         lib = build.load("return_moe", _MOE_SOURCES, {"RB_PDL_MODE": PDL_MODE})
         P, I, F = c_void_p, c_int, c_float
-        lib.rb_moe_route.argtypes = [P, I, P, P, P, I, I, I, I, I, F, P]
+        lib.rb_moe_route.argtypes = [P, I, P, P, P, I, I, I, I, I, F, I, I, F, P]
         lib.rb_moe_pair_linear.argtypes = [P, I, I, P, P, P, I, I, I, I, I, P]
         lib.rb_clamped_glu.argtypes = [P, I, P, I, I, I, I, F, F, F, P]
         lib.rb_moe_combine.argtypes = [P, P, P, P, P, I, I, I, I, P]
@@ -1314,11 +1439,14 @@ def moe_lib() -> ctypes.CDLL:
     return _moe
 
 
-def moe_route(logits, expert_of, weight, top: int, groups: int = 1, keep: int = 1, tiny: float = 1e-20, bias=None) -> None:
+def moe_route(logits, expert_of, weight, top: int, groups: int = 1, keep: int = 1, tiny: float = 1e-20, bias=None,
+              score: str = "softmax", group_top: int = 1, scale: float = 1.0) -> None:
     """The router's choice per token from float32 logits [T, E] (plus ``bias``, float32 [E], if given): softmax over all
     experts; with ``groups`` > 1 only the
     experts of the ``keep`` groups (equal runs of neighbours) with the largest best score can be chosen; the ``top``
-    largest scores among them, in falling order, into expert_of (int32 [T, top]) with weight = score / (sum + tiny)."""
+    largest scores among them, in falling order, into expert_of (int32 [T, top]) with weight = score / (sum + tiny).
+    ``score`` "sigmoid": every expert's score is the logistic of its own logit.  ``group_top`` 2: a group scores as the sum
+    of its two best.  ``scale``: a factor on the weights."""
     T, E = logits.shape
     assert logits.dtype == torch.float32 and logits.stride(1) == 1
     assert expert_of.dtype == torch.int32 and expert_of.shape == (T, top) and expert_of.is_contiguous()
@@ -1326,7 +1454,7 @@ def moe_route(logits, expert_of, weight, top: int, groups: int = 1, keep: int = 
     if bias is not None:
         assert bias.dtype == torch.float32 and bias.numel() == E and bias.is_contiguous()
     _check(moe_lib().rb_moe_route(_ptr(logits), logits.stride(0), _ptr(bias), _ptr(expert_of), _ptr(weight), T, E, top, groups,
-                                  keep, tiny, _stream()), "moe_route")
+                                  keep, tiny, {"softmax": 0, "sigmoid": 1}[score], group_top, scale, _stream()), "moe_route")
 
 
 def moe_pair_linear(x, in_div: int, w, expert_of, out) -> None:

@@ -36,11 +36,16 @@ class DecoderModel:
         # for looking inside a step: called as after_block(schedule index, stream, pending delta) behind every block
         self.after_block = None
         self.lm_head: Optional[torch.Tensor] = None
+        self.embed_pairs: Optional[torch.Tensor] = None
+        if spec.embedding_pairs is not None and spec.streams is not None:
+            raise ValueError("the table of token pairs is added to one residual stream")
 
     # ------------------------------------------------------------------ parameters
     def params(self) -> Dict[str, ParamSpec]:
         s = self.spec
         p = {"embed": ParamSpec((s.vocab_size, s.hidden_size))}
+        if s.embedding_pairs is not None:
+            p["embed_pairs"] = ParamSpec((s.embedding_pairs[0] + 1, s.hidden_size))
         for i, block in enumerate(self.blocks):
             for name, ps in block.params().items():
                 p[f"layers.{i}.{name}"] = ps
@@ -56,6 +61,8 @@ class DecoderModel:
     def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
         self.embed = tensors["embed"]
         self.lm_head = self.embed if self.spec.tie_embeddings else tensors["lm_head"]
+        if self.spec.embedding_pairs is not None:
+            self.embed_pairs = tensors["embed_pairs"]
         for i, block in enumerate(self.blocks):
             prefix = f"layers.{i}."
             block.bind({k[len(prefix):]: v for k, v in tensors.items() if k.startswith(prefix)})
@@ -88,10 +95,14 @@ class DecoderModel:
 
     # ------------------------------------------------------------------ caches
     def cache_needs(self) -> List[object]:
-        """Per schedule entry: what the run's mixer wants cached (None if it owns no cache)."""
+        """Per schedule entry: what the run's mixer wants cached (None if it owns no cache).  A model whose embedding
+        looks at the token before (``DecoderSpec.embedding_pairs``) keeps a request's last token: one more entry
+        behind the schedule's, an int per state slot."""
         out = []
         for e in self.spec.schedule:
             out.append(self.blocks[e.layer].cache_need() if e.cache_of is None else None)
+        if self.spec.embedding_pairs is not None:
+            out.append(StateNeed((1,), torch.int32))
         return out
 
     @staticmethod
@@ -109,7 +120,14 @@ class DecoderModel:
         dev = self.env.device
         S = self.spec.streams
         stream = torch.empty((T, H) if S is None else (T, S, H), dtype=torch.float32, device=dev)
-        ops.embedding(self.embed, batch.tokens, stream, self.spec.embedding_scale)
+        if self.spec.embedding_pairs is None:
+            ops.embedding(self.embed, batch.tokens, stream, self.spec.embedding_scale)
+        else:
+            buckets, mul_prev, mul_cur = self.spec.embedding_pairs
+            last = storage.layer_context(len(self.spec.schedule), batch, write=True).state
+            ops.embedding_pair(self.embed, self.embed_pairs, batch, last, stream, self.spec.embedding_scale, buckets,
+                               mul_prev, mul_cur)
+            ops.last_token_update(batch, last)             # after every token of the step has read the old one
         if self.embedding_norm is not None:
             self.embedding_norm.forward(stream, stream)           # in place: a warp reads its row before it writes it
         delta = None

@@ -18,11 +18,19 @@ class PreNormBlock(Block):
     def __init__(self, spec, env):
         super().__init__(spec, env)
         self.mixer = MIXERS.build(spec.mixer, env)
-        self.feed_forward = FEED_FORWARDS.build(spec.feed_forward, env)
+        self.feed_forward = FEED_FORWARDS.build(spec.feed_forward, env) if spec.feed_forward is not None else None
         self.mixer_norm = NORMS.build(spec.mixer_norm, env)
-        self.feed_forward_norm = NORMS.build(spec.feed_forward_norm, env)
-        self._children = {"mixer": self.mixer, "feed_forward": self.feed_forward,
-                          "mixer_norm": self.mixer_norm, "feed_forward_norm": self.feed_forward_norm}
+        self.feed_forward_norm = NORMS.build(spec.feed_forward_norm, env) if spec.feed_forward is not None else None
+        self.residual_scale = float(getattr(spec, "residual_scale", 1.0))
+        self._children = {"mixer": self.mixer, "mixer_norm": self.mixer_norm}
+        if self.feed_forward is not None:
+            self._children.update({"feed_forward": self.feed_forward, "feed_forward_norm": self.feed_forward_norm})
+        # a sublayer's output times a factor, or a layer without a feed-forward: the adds run in the kernel that takes
+        # a factor per addend (csrc/recurrent.cu, add_dual_norm), which wants RMSNorms
+        self._scaled = self.residual_scale != 1.0 or self.feed_forward is None
+        if self._scaled and any(getattr(n.spec, "kind", None) != "rmsnorm" for n in (self.mixer_norm, self.feed_forward_norm)
+                                if n is not None):
+            raise ValueError("a pre-norm block with a residual factor, or without a feed-forward, has RMSNorms")
 
     @property
     def graph_safe(self):
@@ -67,7 +75,7 @@ class PreNormBlock(Block):
         and leaves v * w and sum(v^2); the product after it (the gated one, the next block's first) scales by
         rstd (csrc/gemm_skinny.cu).  Six launches a layer instead of eight.  That needs a mixer and a feed-forward
         that expose their products, RMSNorms, and sizes the kernel takes; anything else runs part by part."""
-        if self.env.act_dtype != torch.bfloat16 or stream.shape[0] > ops.SKINNY_MAX_ROWS:
+        if self.env.act_dtype != torch.bfloat16 or stream.shape[0] > ops.SKINNY_MAX_ROWS or self._scaled:
             return None
         plan = getattr(self, "_fused_parts", None)
         if plan is None:
@@ -119,7 +127,34 @@ class PreNormBlock(Block):
             held["block.prenormed"] = {"rows": rows3, "sums": sums3, "position": ctx.position + 1}
         return None                                            # the stream already holds this block's output
 
+    def _forward_scaled(self, stream, delta, ctx):
+        """x += m * mixer(norm(x)); x += m * feed_forward(norm(x)).  Every add is fused with the norm that follows it,
+        the last one with the first norm of the block that runs next when that block is of this kind (its normed rows
+        are left under ``block.prenormed_rows`` in the step's scratch); the block owes the stream nothing."""
+        T, H = stream.shape
+        m = self.residual_scale
+        n1, n2 = self.mixer_norm, self.feed_forward_norm
+        held = getattr(ctx.batch, "scratch", None)
+        pre = held.pop("block.prenormed_rows", None) if held is not None else None
+        a = ctx.buffer("block.normed", (T, H), self.env.act_dtype, stream.device)
+        if not (delta is None and pre is not None and pre["position"] == ctx.position and pre["rows"] is a):
+            ops.add_dual_norm(stream, (delta,), n1.p_weight, None, n1.spec.eps, n1.spec.offset, a, None)
+        y = self.mixer.forward(a, ctx)
+        if self.feed_forward is not None:
+            ops.add_dual_norm(stream, (y,), n2.p_weight, None, n2.spec.eps, n2.spec.offset, a, None, scales=(m, 1.0))
+            y = self.feed_forward.forward(a, ctx)
+        nxt = ctx.next_block
+        if held is not None and isinstance(nxt, PreNormBlock) and nxt._scaled and nxt.mixer_norm.spec.size == H:
+            n = nxt.mixer_norm
+            ops.add_dual_norm(stream, (y,), n.p_weight, None, n.spec.eps, n.spec.offset, a, None, scales=(m, 1.0))
+            held["block.prenormed_rows"] = {"rows": a, "position": ctx.position + 1}
+        else:
+            ops.add_dual_norm(stream, (y,), None, None, 0.0, 0.0, None, None, scales=(m, 1.0))
+        return None
+
     def forward(self, stream, delta, ctx):
+        if self._scaled:
+            return self._forward_scaled(stream, delta, ctx)
         plan = self._fused_plan(stream) if getattr(ctx.batch, "scratch", None) is not None else None
         if plan is not None:
             return self._forward_fused(plan, stream, delta, ctx)

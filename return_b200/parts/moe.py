@@ -56,6 +56,8 @@ class MixtureOfExperts(FeedForward):
             raise ValueError(f"{s.num_experts} experts do not form {s.groups} equal groups of which {s.keep_groups} are kept")
         if not (1 <= s.top <= s.keep_groups * (s.num_experts // s.groups)):
             raise ValueError(f"top={s.top} experts cannot be chosen from {s.keep_groups} groups of {s.num_experts // s.groups}")
+        if s.score not in ("softmax", "sigmoid") or s.group_top not in (1, 2):
+            raise ValueError("score is 'softmax' or 'sigmoid'; a group is ranked by its best score or its two best")
         self.shared = FEED_FORWARDS.build(s.shared, env) if s.shared is not None else None
 
     @property
@@ -89,7 +91,8 @@ class MixtureOfExperts(FeedForward):
         ops.linear(x, self.p_router, logits)
         expert_of = work_buffer(ctx, "moe.expert_of", (T, s.top), torch.int32, dev)
         weight = work_buffer(ctx, "moe.weight", (T, s.top), torch.float32, dev)
-        ops.moe_route(logits, expert_of, weight, s.top, s.groups, s.keep_groups, s.renorm_tiny, bias=self.router_bias)
+        ops.moe_route(logits, expert_of, weight, s.top, s.groups, s.keep_groups, s.renorm_tiny, bias=self.router_bias,
+                      score=s.score, group_top=s.group_top, scale=s.weight_scale)
         shared = self.shared.forward(x, ctx) if self.shared is not None else None
         y = work_buffer(ctx, "moe.y", (T, s.hidden_size), dt, dev)
         limit, alpha, shift = self.unit

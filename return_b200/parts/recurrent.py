@@ -391,3 +391,127 @@ class StateSpace(_StateMixer):
         mixed = ctx.buffer("state_space.mixed", (T, inner), x.dtype, dev)
         ops.gated_part_norm(y, proj[:, :inner], self.p_norm, s.norm_groups, s.eps, mixed)
         return self._project_out(mixed, ctx)
+
+
+@MIXERS.register("gated_delta")
+class GatedDelta(_StateMixer):
+    """``GatedDeltaSpec``: the delta rule with one decay a head.  The request's state row holds S and then the last
+    ``conv_taps - 1`` inputs of every convolved channel."""
+
+    def __init__(self, spec, env):
+        super().__init__(spec, env)
+        self._sizes()
+        s = spec
+        if s.num_heads % s.num_kv_heads:
+            raise ValueError(f"num_heads={s.num_heads} is not a multiple of num_kv_heads={s.num_kv_heads}")
+        if not (1 <= s.conv_taps <= 33):
+            raise ValueError("conv_taps: 1 to 33")
+        if s.unit_eps != 1e-6:
+            raise ValueError("the kernel's unit vectors use 1e-6 under the root")
+        self.G = s.num_kv_heads
+        self.channels = 2 * self.G * self.D + self.H * self.V
+        self.conv_off = self.s_floats
+
+    def params(self):
+        s = self.spec
+        C, HV = self.channels, self.H * self.V
+        return {"in": ParamSpec((C + HV, s.hidden_size)),                                 # q, k, v, output gate
+                "conv": ParamSpec((C, s.conv_taps), role="vector", init="normal:0.5"),
+                "beta": ParamSpec((self.H, s.hidden_size)),
+                "decay": ParamSpec((self.H, s.hidden_size)),
+                "A_log": ParamSpec((self.H,), role="vector", init="normal:0.5"),
+                "dt_bias": ParamSpec((self.H,), role="vector", init="normal:0.5"),
+                "norm": ParamSpec((self.V,), role="vector", init="ones_normal"),
+                "o": ParamSpec((s.hidden_size, HV))}
+
+    def cache_need(self):
+        return StateNeed((self.s_floats + self.channels * (self.spec.conv_taps - 1),), torch.float32)
+
+    def forward(self, x, ctx):
+        s, b = self.spec, ctx.batch
+        T, dev = x.shape[0], x.device
+        C, GD, HV = self.channels, self.G * self.D, self.H * self.V
+        proj = ctx.buffer("gated_delta.in", (T, C + HV), x.dtype, dev)
+        ops.linear(x, self.p_in, proj)
+        beta = ctx.buffer("gated_delta.beta", (T, self.H), torch.float32, dev)
+        ops.linear(x, self.p_beta, beta)
+        decay = ctx.buffer("gated_delta.decay", (T, self.H), torch.float32, dev)
+        ops.linear(x, self.p_decay, decay)
+        q32 = ctx.buffer("gated_delta.q", (T, GD), torch.float32, dev)
+        k32 = ctx.buffer("gated_delta.k", (T, GD), torch.float32, dev)
+        v32 = ctx.buffer("gated_delta.v", (T, HV), torch.float32, dev)
+        ops.delta_prep(proj, self.p_conv, ctx.state, self.conv_off, b, q32, k32, v32, decay, self.p_A_log,
+                       self.p_dt_bias, beta, self.H, self.G, self.D, self.V, self.D ** -0.5, head_decay=True)
+        ops.conv_state_update(proj, s.conv_taps, ctx.state, self.conv_off, b, C)      # after every token read the old one
+        o = ctx.buffer("gated_delta.o", (T, HV), torch.float32, dev)
+        ops.linear_scan(ops.SCAN_DELTA_HEAD, q32, k32, v32, decay, beta, ctx.state, (0, 0, 0), b, o,
+                        self.H, self.G, self.D, self.V)
+        mixed = ctx.buffer("gated_delta.mixed", (T, HV), x.dtype, dev)
+        ops.head_norm_gate(o, proj[:, C:], self.p_norm, 1, 0, s.eps, mixed, self.H, self.V)
+        return self._project_out(mixed, ctx)
+
+
+@MIXERS.register("gated_linear_recurrence")
+class GatedLinearRecurrence(Mixer):
+    """``GatedLinearRecurrenceSpec``: one product gives [y | x]; a kernel convolves x over time (reading the request's
+    held inputs before the step's first token); two batched products over the blocks give the gates' pre-activations in
+    float32; a kernel walks every segment token by token, one thread a channel, and leaves s * gelu_tanh(y); the
+    output projection follows.  The request's state row holds s [width] and then the last ``conv_taps - 1`` inputs of
+    every channel (kept without their bias)."""
+
+    def __init__(self, spec, env):
+        super().__init__(spec, env)
+        s = spec
+        if s.blocks < 1 or s.width % s.blocks:
+            raise ValueError(f"width={s.width} does not form {s.blocks} equal blocks")
+        if not (1 <= s.conv_taps <= 33):
+            raise ValueError("conv_taps: 1 to 33")
+        self.W, self.bs = s.width, s.width // s.blocks
+        self.conv_off = self.W
+
+    def params(self):
+        s = self.spec
+        W, B, bs = self.W, s.blocks, self.bs
+        return {"in": ParamSpec((2 * W, s.hidden_size)),                                  # y rows, then x rows
+                "in_bias": ParamSpec((2 * W,), role="vector", init="normal:0.2"),
+                "conv": ParamSpec((W, s.conv_taps), role="vector", init="normal:0.5"),
+                "conv_bias": ParamSpec((W,), role="vector", init="normal:0.2"),
+                "gate_r": ParamSpec((B, bs, bs), init="fan_in"), "gate_i": ParamSpec((B, bs, bs), init="fan_in"),
+                "gate_r_bias": ParamSpec((B, bs), role="vector", init="normal:0.5"),
+                "gate_i_bias": ParamSpec((B, bs), role="vector", init="normal:0.5"),
+                "lam": ParamSpec((W,), role="vector", init="normal:0.5"),
+                "o": ParamSpec((s.hidden_size, W))}
+
+    def bind(self, tensors):
+        super().bind(tensors)
+        # the small vectors share one type, whatever the file stores each in
+        dt = torch.float32 if any(tensors[n].dtype == torch.float32 for n in
+                                  ("in_bias", "conv", "conv_bias", "gate_r_bias", "gate_i_bias", "lam")) else self.env.act_dtype
+        for n in ("in_bias", "conv", "conv_bias", "gate_r_bias", "gate_i_bias", "lam"):
+            setattr(self, "p_" + n, tensors[n].to(dt).contiguous())
+
+    def cache_need(self):
+        return StateNeed((self.W + self.W * (self.spec.conv_taps - 1),), torch.float32)
+
+    def out_projection(self):
+        return self.p_o
+
+    def forward(self, x, ctx):
+        s, b = self.spec, ctx.batch
+        T, dev, dt = x.shape[0], x.device, x.dtype
+        W, B, bs = self.W, s.blocks, self.bs
+        proj = ctx.buffer("gated_linear_recurrence.in", (T, 2 * W), dt, dev)
+        ops.linear(x, self.p_in, proj)
+        u = ctx.buffer("gated_linear_recurrence.u", (T, W), dt, dev)
+        ops.gated_conv(proj[:, W:], self.p_in_bias[W:], self.p_conv, self.p_conv_bias, ctx.state, self.conv_off, b, u)
+        ops.conv_state_update(proj[:, W:], s.conv_taps, ctx.state, self.conv_off, b, W)  # after every token read the old one
+        gates = ctx.buffer("gated_linear_recurrence.gates", (2, B, T, bs), torch.float32, dev)
+        ub = u.view(T, B, bs).transpose(0, 1)
+        ops.linear_heads(ub, self.p_gate_r, gates[0])
+        ops.linear_heads(ub, self.p_gate_i, gates[1])
+        mixed = ctx.buffer("gated_linear_recurrence.mixed", (T, W), dt, dev)
+        ops.gated_recurrence(u, gates, bs, self.p_gate_r_bias, self.p_gate_i_bias, self.p_lam, float(s.decay_scale),
+                             proj, self.p_in_bias[:W], ctx.state, 0, b, mixed)
+        y = ctx.buffer("gated_linear_recurrence.y", (T, s.hidden_size), torch.float32, dev)
+        ops.linear(mixed, self.p_o, y)
+        return y

@@ -151,3 +151,33 @@ class RampedRotaryEncoding(PositionEncoding):
 def drop_shared_tables() -> None:
     """Forgets the shared tables (models that still hold them keep them alive)."""
     _TABLES.clear()
+
+
+@POSITION_ENCODINGS.register("rope_interleaved")
+class InterleavedRotaryEncoding(PositionEncoding):
+    """Tables for a rotation of neighbouring pairs (``InterleavedRopeSpec``): column i of cos and sin belongs to the
+    elements 2i and 2i + 1 of a head.  Frequencies and angles are worked out in float64 on the host and rounded once.
+    The rotation itself happens in the kernel that prepares an attention's rows (csrc/attention_prep.cu)."""
+
+    interleaved = True
+
+    def __init__(self, spec, env):
+        super().__init__(spec, env)
+        if spec.rotary_dim % 2 or spec.rotary_dim <= 0:
+            raise ValueError(f"rotary_dim={spec.rotary_dim} must be even and positive")
+        self._tables = None
+
+    def tables(self):
+        """(cos, sin, rotary_dim); cos and sin are float32 [max_positions, rotary_dim / 2] on the device."""
+        if self._tables is None:
+            s = self.spec
+            key = ("interleaved", s.rotary_dim, float(s.theta), s.max_positions, str(self.env.device))
+            shared = _TABLES.get(key)
+            if shared is None:
+                half = s.rotary_dim // 2
+                f = float(s.theta) ** (-2.0 * torch.arange(0, half, dtype=torch.float64) / s.rotary_dim)
+                ang = torch.outer(torch.arange(s.max_positions, dtype=torch.float64), f)
+                shared = _TABLES[key] = (ang.cos().float().contiguous().to(self.env.device),
+                                         ang.sin().float().contiguous().to(self.env.device), s.rotary_dim)
+            self._tables = shared
+        return self._tables

@@ -66,6 +66,17 @@ class RampedRopeSpec:
 
 
 @dataclass(frozen=True)
+class InterleavedRopeSpec:
+    """Rotary encoding of the first ``rotary_dim`` elements of a head in which element 2i is paired with element 2i + 1:
+    the pair (u, v) at position p becomes (u cos a - v sin a, v cos a + u sin a), a = p * theta^(-2i / rotary_dim).
+    Tables are worked out in float64."""
+    rotary_dim: int
+    theta: float
+    max_positions: int
+    kind: str = "rope_interleaved"
+
+
+@dataclass(frozen=True)
 class LatentAttentionSpec:
     """Causal attention whose keys and values are linear maps of one cached latent a token.  Per head: ``key_dim``
     unrotated query/key elements, ``rot_dim`` rotated ones (the rotated key part is one vector shared by all heads,
@@ -110,6 +121,42 @@ class AttentionSpec:
 
 
 @dataclass(frozen=True)
+class GatedAttentionSpec:
+    """Causal grouped-query attention over a paged cache whose heads are prepared row by row, with an output gate.
+    Heads have ``key_dim`` query/key elements and ``value_dim`` value elements (the cache holds both padded to one size).
+    Options, each off unless given: ``bias`` (q, k, v projections have biases); ``whole_norm_eps`` (an RMS norm with a
+    weight per element over the whole q projection and over the whole k projection, before the rotation);
+    ``position`` (an ``InterleavedRopeSpec``: q and k are rotated, values are not); ``values_are_keys`` (there is no value
+    projection: a value is the key projection as it comes out of the product, before norm and rotation);
+    ``window`` (a query sees the last n keys, its own included) or ``chunk`` (a query sees the earlier keys of its own block
+    of n positions, blocks counted from position 0); ``softcap`` (a scaled score s becomes cap tanh(s / cap));
+    ``slope_exponent`` e (slope_h (i - j) is taken off the score, slope_h = 2^(-e (h + 1) / heads)); ``sink`` (a learned
+    number per head whose exponential joins the softmax's denominator); ``gate`` "head" (a head's output times the
+    logistic of one projected number) or "element" (one per value element).  ``own_cache`` False: the layer has no key
+    and value projections and reads the cache that another run of the schedule wrote.  ``cache_window``: how many of the
+    latest keys the cache must keep for this layer and every layer that reads its cache (None: all)."""
+    hidden_size: int
+    num_heads: int
+    num_kv_heads: int
+    key_dim: int
+    value_dim: int
+    scale: float
+    bias: bool = False
+    whole_norm_eps: Optional[float] = None
+    position: Optional[Any] = None
+    values_are_keys: bool = False
+    window: Optional[int] = None
+    chunk: Optional[int] = None
+    softcap: Optional[float] = None
+    slope_exponent: Optional[float] = None
+    sink: bool = False
+    gate: Optional[str] = None
+    own_cache: bool = True
+    cache_window: Optional[int] = None
+    kind: str = "gated_attention"
+
+
+@dataclass(frozen=True)
 class RetentionSpec:
     """Linear attention with one fixed decay a head and no softmax: S <- decay S + k v^T, o = S^T q; q and k are
     rotated (``position``), k is scaled by key_dim^-1/2; each head's o is divided by its root mean square, gated
@@ -141,6 +188,39 @@ class ChannelDeltaSpec:
     eps: float
     unit_eps: float = 1e-6
     kind: str = "channel_delta"
+
+
+@dataclass(frozen=True)
+class GatedDeltaSpec:
+    """Gated delta rule with one decay per head and token.  q, k (``num_kv_heads`` heads of ``key_dim``) and v
+    (``num_heads`` heads of ``value_dim``) pass a causal convolution of ``conv_taps`` taps and silu; q and k become unit
+    vectors (``unit_eps`` under the root), q times key_dim^-1/2; beta = sigmoid of a projection; the decay is
+    g = exp(-exp(A_log) softplus(projection + dt_bias)); per head S <- g S, u = beta (v - S^T k), S <- S + k u^T,
+    o = S^T q; o is normed per head, weighted by a weight of size value_dim shared by the heads, gated by silu of a
+    projection, and projected out."""
+    hidden_size: int
+    num_heads: int
+    num_kv_heads: int
+    key_dim: int
+    value_dim: int
+    conv_taps: int
+    eps: float
+    unit_eps: float = 1e-6
+    kind: str = "gated_delta"
+
+
+@dataclass(frozen=True)
+class GatedLinearRecurrenceSpec:
+    """A recurrent branch beside a gate branch, both ``width`` wide.  y = gelu_tanh(W_y x + b_y); u = conv(W_x x + b_x), a
+    causal convolution of ``conv_taps`` taps per channel with a bias; u is cut into ``blocks`` equal parts, and in each
+    part two square maps with biases give r = sigmoid(.) and i = sigmoid(.); log f = -``decay_scale`` r softplus(lam);
+    per channel s <- f s + sqrt(1 - f^2) i u from s = 0; the output is W_o (s * y)."""
+    hidden_size: int
+    width: int
+    blocks: int
+    conv_taps: int
+    decay_scale: float = 8.0
+    kind: str = "gated_linear_recurrence"
 
 
 @dataclass(frozen=True)
@@ -252,7 +332,9 @@ class MoESpec:
     can be chosen; the chosen scores divided by their sum (+ ``renorm_tiny``) weigh the experts' outputs (with
     ``renorm_tiny`` = 0 that is the softmax over the chosen logits alone).  ``router_bias``: a bias per expert is added to
     the logits.  ``expert`` is a ``ClampedGLUSpec`` or a ``SwiGLUSpec`` with rows not woven.  ``shared``: a feed-forward
-    that runs for every token and is added, or None."""
+    that runs for every token and is added, or None.  ``score`` "sigmoid": every expert's score is the logistic of its own
+    logit instead of a softmax over all.  ``group_top`` 2: a group is ranked by the sum of its two largest scores instead of
+    its largest.  ``weight_scale``: a factor on the weights after they were divided by their sum."""
     hidden_size: int
     num_experts: int
     top: int
@@ -263,6 +345,9 @@ class MoESpec:
     renorm_tiny: float = 1e-20
     router_bias: bool = False
     kind: str = "moe"
+    score: str = "softmax"
+    group_top: int = 1
+    weight_scale: float = 1.0
 
 
 @dataclass(frozen=True)
@@ -296,12 +381,14 @@ class HyperBlockSpec:
 
 @dataclass(frozen=True)
 class BlockSpec:
-    """The arrangement of one layer: x += mixer(norm(x)); x += feed_forward(norm(x))."""
+    """The arrangement of one layer: x += m * mixer(norm(x)); x += m * feed_forward(norm(x)), with m =
+    ``residual_scale``.  ``feed_forward`` None: the layer has none (and no norm for it)."""
     mixer: Any
     feed_forward: Any
     mixer_norm: Any
     feed_forward_norm: Any
     kind: str = "prenorm"
+    residual_scale: float = 1.0
 
 
 @dataclass(frozen=True)
@@ -323,6 +410,10 @@ class DecoderSpec:
     embedding_norm: Any = None            # a norm applied to the embedded tokens before the first layer
     logit_softcap: Optional[float] = None  # logits <- cap * tanh(logits / cap)
     embedding_scale: float = 1.0          # the embedded tokens are multiplied by this (the output head is not)
+    # (buckets, mul_prev, mul_cur): a table ``embed_pairs`` [buckets + 1, hidden] adds the row
+    # (previous token * mul_prev + token * mul_cur) mod buckets to an embedded token (after the scale), and its last row
+    # to a sequence's first token; a request's last token is then part of its state
+    embedding_pairs: Optional[Tuple[int, int, int]] = None
     streams: Optional[int] = None         # None: one residual stream [T, hidden].  n: a token has n streams
                                           # ([T, n, hidden]; every block must take them), all start as the embedded
                                           # token and their sum goes to the final norm
