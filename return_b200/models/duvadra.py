@@ -101,7 +101,8 @@ def decoder_spec(cfg: DuvadraConfig, max_positions: Optional[int] = None) -> Dec
     for i, layer in enumerate(cfg.layers):
         ff = _mlp_spec(layer.get("mlp"), W)
         blocks.append(BlockSpec(mixer=_mixer_spec(cfg, i, windows, max_positions), feed_forward=ff, mixer_norm=norm,
-                                feed_forward_norm=norm if ff is not None else None, residual_scale=cfg.residual_mult))
+                                feed_forward_norm=norm if ff is not None else None, residual_scale=cfg.residual_mult,
+                                float_outputs=True))
         src = layer["mixer"].get("kv_from") if layer["type"] == "attention" else None
         schedule.append(ScheduleEntry(i, cache_of=int(src) if src is not None else None))
     return DecoderSpec(vocab_size=cfg.vocab, hidden_size=W, layers=tuple(blocks), schedule=tuple(schedule), final_norm=norm,

@@ -27,7 +27,7 @@ class PreNormBlock(Block):
             self._children.update({"feed_forward": self.feed_forward, "feed_forward_norm": self.feed_forward_norm})
         # a sublayer's output times a factor, or a layer without a feed-forward: the adds run in the kernel that takes
         # a factor per addend (csrc/recurrent.cu, add_dual_norm), which wants RMSNorms
-        self._scaled = self.residual_scale != 1.0 or self.feed_forward is None
+        self._scaled = (self.residual_scale != 1.0 or self.feed_forward is None or bool(getattr(spec, "float_outputs", False)))
         if self._scaled and any(getattr(n.spec, "kind", None) != "rmsnorm" for n in (self.mixer_norm, self.feed_forward_norm)
                                 if n is not None):
             raise ValueError("a pre-norm block with a residual factor, or without a feed-forward, has RMSNorms")

@@ -389,6 +389,8 @@ class BlockSpec:
     feed_forward_norm: Any
     kind: str = "prenorm"
     residual_scale: float = 1.0
+    float_outputs: bool = False           # the sublayers may hand back float32 on the bfloat16 path (the adds then run in
+                                          # the kernel that takes either type)
 
 
 @dataclass(frozen=True)
