@@ -126,7 +126,7 @@ RB_EXPORT int rb_attn_prep(const void* proj, int ld, int q_off, int k_off, int v
                            const int* block_table, int bt_stride, int page_size, void* kpool, void* vpool, void* q_out,
                            int act_dtype, int T, int Hq, int Hkv, int dim, int vdim, int D, int write_kv, cudaStream_t st) {
     if (T <= 0) return 0;
-    if (D % 2 || dim > D || vdim > D || rot % 2 || rot > dim || (v_off < 0 && vdim > dim)) return (int)cudaErrorInvalidValue;
+    if (D % 2 || dim > D || vdim > D || rot % 2 || rot > dim || (write_kv && v_off < 0 && vdim > dim)) return (int)cudaErrorInvalidValue;
     PrepArgs a;
     a.proj = proj; a.ld = ld; a.q_off = q_off; a.k_off = k_off; a.v_off = v_off;
     a.q_bias = q_bias; a.k_bias = k_bias; a.v_bias = v_bias; a.bias_dtype = bias_dtype;

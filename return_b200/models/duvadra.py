@@ -165,8 +165,9 @@ def weight_sources(cfg: DuvadraConfig) -> Dict[str, Source]:
 
 def checkpoint_shapes(cfg: DuvadraConfig) -> Dict[str, Tuple[Tuple[int, ...], str]]:
     """Every tensor of a checkpoint: name -> (shape, law of its random values).  Matrices are drawn with a deviation of
-    fan_in^-1/2 (half that for the maps back into the stream, twelve times that for the routers, so that rounding seldom
-    turns a choice), norm weights around one, the others so that gates, decays and sinks are neither shut nor open."""
+    fan_in^-1/2 (half that for the maps back into the stream, three times that for the routers: logistic scores far apart
+    without running into one), norm weights around one, the others so that gates, decays and sinks are neither shut nor
+    open."""
     W, V = cfg.width, cfg.vocab
     out: Dict[str, Tuple[Tuple[int, ...], str]] = {"embed": ((V, W), "normal:1.0"), "final.norm": ((W,), "ones_normal"),
                                                    "head": ((V, W), "fan_in")}
@@ -241,7 +242,7 @@ def checkpoint_shapes(cfg: DuvadraConfig) -> Dict[str, Tuple[Tuple[int, ...], st
                 out[z + "down"] = ((W, ff), "fan_in:0.5")
             else:
                 E, F = int(mlp["router"]["experts"]), int(mlp["expert"]["ff"])
-                out[z + "router"] = ((E, W), "fan_in:12")           # choices that rounding seldom turns
+                out[z + "router"] = ((E, W), "fan_in:3")
                 for j in range(E):
                     out[f"{z}e{j}.gate"] = ((F, W), "fan_in")
                     out[f"{z}e{j}.up"] = ((F, W), "fan_in")

@@ -378,14 +378,19 @@ def _slow_decays(tensors):
 
 
 def sharp_config(kind, size=37):
-    """A first layer without a feed-forward whose attention scores are eight times larger than usual, so that single
-    keys stand out; no pair table, so that a token's query and key in that layer depend on the token alone."""
+    """One layer without a feed-forward whose attention scores are eight times larger than usual, so that single
+    keys stand out; no pair table, so that a token's query and key depend on the token alone."""
     if kind == "block":
         first = chunk_layer(heads=2, kv_heads=1, dim=16, vdim=16, size=size, scale=8 * 16 ** -0.5, softcap=60.0, mlp=None)
     else:
         first = delta_layer(left=attn(heads=2, kv_heads=1, dim=16, vdim=16, size=size, scale=8 * 16 ** -0.5), heads=2, kv_heads=1,
                             dim=16, vdim=16, scales=(1.0, 0.2), mlp=None)
-    return config([first, lru_layer(mlp=None), delta_layer(mlp=None)], width=32, bigram=None, mult=1.0)
+    return config([first], width=32, bigram=None, mult=1.0, cap=None, scale=0.25)
+
+
+def slow_states_config():
+    """Both state mixers, weighing far more than the windowed attentions beside them, with the pair table."""
+    return config([delta_layer(scales=(0.2, 1.5), mlp=None), lru_layer(scales=(0.2, 1.5), mlp=None)], width=32, mult=1.0)
 
 
 def _standing_out_pair(c, w, kind):
@@ -453,7 +458,7 @@ def test_keys_just_inside_and_outside_a_window_and_a_block(tmp_path_factory, kin
     want = plain_rows(entry, ids)
     fewer = row_errors(_with_bound_moved(entry, +1)(ids), want)
     more = row_errors(_with_bound_moved(entry, -1)(ids), want)
-    assert float(fewer[inside].min()) > 2 * TOL[dtype] and float(more[outside].min()) > 2 * TOL[dtype]
+    assert float(fewer[inside].min()) > 0.15 and float(more[outside].min()) > 0.15
     reqs = {"edge": ids}
     for steps, page in ((whole(reqs), 16), (tail_decoded(reqs, tail=130), 8),
                         (portions(reqs, [36, 2, 37, 1, 38, 3, 33]), 4),
@@ -468,13 +473,13 @@ def test_keys_just_inside_and_outside_a_window_and_a_block(tmp_path_factory, kin
 def test_states_far_back_and_at_page_borders(tmp_path_factory, dtype):
     """Every attention of the design forgets behind its window or block; what reaches further is the states.  With slow
     decays the last rows lean on the first two hundred tokens: without them the plain model gives other rows."""
-    entry = model(tmp_path_factory, "sharp_window", sharp_config("window"), patch=_slow_decays)
+    entry = model(tmp_path_factory, "slow_states", slow_states_config(), patch=_slow_decays)
     ids = requests_for(entry, (330,), seed=6)["r0"]
     want = plain_rows(entry, ids)
     c, w = entry[1]
     short = plain.forward(c, w, ids[200:]).float()
     lost = row_errors(short[-20:], want[-20:])
-    assert float(lost.min()) > TOL[dtype] and float(lost.mean()) > 3 * TOL[dtype]
+    assert float(lost.mean()) > 0.08
     reqs = {"far": ids}
     for steps, page in ((tail_decoded(reqs, tail=36), 16), (portions(reqs, [250, 6, 10, 2, 62]), 8)):
         got = run_trace(entry[0], dtype, steps, page_size=page)["far"]
@@ -485,13 +490,12 @@ def test_states_far_back_and_at_page_borders(tmp_path_factory, dtype):
 def test_a_slot_taken_again_inherits_nothing(tmp_path_factory):
     """Two requests one after the other through one slot: the second starts from zero states, zero conv inputs and no
     token before its first (the plain walk of the second alone), although the first left states that hardly decay."""
-    raw = config([delta_layer(mlp=None), lru_layer(mlp=None)], width=32)
-    entry = model(tmp_path_factory, "slow_states", raw, patch=_slow_decays)
+    entry = model(tmp_path_factory, "slow_states", slow_states_config(), patch=_slow_decays)
     reqs = requests_for(entry, (50, 30), seed=12)
     for dtype in ("float32", "bfloat16"):
         compare(entry, dtype, portions(reqs, [7, 1, 20]), reqs, max_reside=1)
     joined = plain_rows(entry, reqs["r0"] + reqs["r1"])[50:]
-    assert float(row_errors(joined, plain_rows(entry, reqs["r1"])).min()) > 2 * TOL["bfloat16"]      # inheriting would show
+    assert float(row_errors(joined, plain_rows(entry, reqs["r1"])).mean()) > 0.08                    # inheriting would show
 
 
 @pytest.mark.parametrize("dtype,graph", [("float32", False), ("bfloat16", True)])
