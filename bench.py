@@ -92,9 +92,9 @@ def main():
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--only", default="all", choices=["all", "decode", "prefill"],
                     help="a reduced run for profiling: only the decode steps, or only the prefill")
-    ap.add_argument("--design", default=None, choices=["pisatar", "gonozen", "nozizen"],
+    ap.add_argument("--design", default=None, choices=["pisatar", "gonozen", "nozizen", "duvadra"],
                     help="instead of the default workload: prefill and decode throughput of this design beside the Qwen3 "
-                         "decoder (nozizen: beside the Pisatar decoder) at equal layer sizes (--sizes), random weights, "
+                         "decoder (nozizen: beside the Pisatar decoder; duvadra: beside the Nozizen decoder) at equal layer sizes (--sizes), random weights, "
                          "one JSON line")
     ap.add_argument("--sizes", default="1k,2k", help="with --design: names of return_b200.benchmark.DESIGN_SIZES")
     ap.add_argument("--kernels", action="store_true",
@@ -121,9 +121,9 @@ def main():
         hbm_gbs, bf16_tflops, peak_src = peaks()
         clocks = ClockSampler()
         clocks.start()
-        compare = {"gonozen": benchmark.compare_gonozen, "nozizen": benchmark.compare_nozizen}.get(args.design, benchmark.compare_designs)
-        beside = "Pisatar at equal width, feed-forward, layers and heads" if args.design == "nozizen" else \
-            "Qwen3 at equal width, feed-forward, layers and heads"
+        compare = {"gonozen": benchmark.compare_gonozen, "nozizen": benchmark.compare_nozizen,
+                   "duvadra": benchmark.compare_duvadra}.get(args.design, benchmark.compare_designs)
+        beside = {"nozizen": "Pisatar", "duvadra": "Nozizen"}.get(args.design, "Qwen3") + " at equal width, feed-forward, layers and heads"
         rows = [compare(size, PROMPT_LEN, args.batch, K, W, hbm_gbs, bf16_tflops) for size in args.sizes.split(",")]
         print(json.dumps({"design": args.design, "beside": beside,
                           "dtype": "bf16", "data": "synthetic: random weights, uniform random token ids", "steps": K,

@@ -783,3 +783,113 @@ def compare_nozizen(size: str, tokens: int, batch: int, steps: int, warmup: int,
         del r["prefill_kernels"], r["decode_kernels"]
     return {"size": size, "width": W, "ff": ff, "heads": H, "kv_heads": G, "layers": L, "tokens": tokens, "batch": batch,
             "streams": S, "window": window, "nozizen": new, "pisatar": old, "kernels": kernels}
+
+
+def duvadra_raw_config(width: int, ff: int, heads: int, kv_heads: int, layers: int, vocab: int, window: int = 1024,
+                       block: int = 8192) -> dict:
+    """A Duvadra configuration whose mixers carry as many heads of 128 as the attention of a Qwen3 model of this width: of
+    every four layers the first is an attention inside blocks of ``block`` positions (soft cap, distance slopes, a gate a
+    head), the second a windowed attention whose values are its keys (rotation over half a head) beside a gated linear
+    recurrence as wide as the model in blocks of 128, the third a block attention on the first layer's keys and values,
+    the fourth a windowed attention with a sink beside a gated delta rule (states of 128 x 128, four taps); the first and
+    fourth feed-forwards are capped gated units, the others 32 experts of a quarter of the dense size each in 8 groups of
+    which 4 are kept, four experts a token, so that a token's experts do the dense feed-forward's work."""
+    dense = {"kind": "dense", "ff": ff, "limit": 7.0}
+    experts = {"kind": "moe", "router": {"experts": 32, "top": 4, "scale": 2.5, "groups": {"count": 8, "keep": 4}},
+               "expert": {"ff": ff // 4}}
+    att = {"heads": heads, "kv_heads": kv_heads, "dim": 128, "vdim": 128, "scale": 128 ** -0.5}
+    blocks = {"type": "attention", "mixer": dict(att, softcap=50.0, mask={"size": block})}
+    lru = {"type": "parallel_2", "mixer": {"left": dict(att, mask={"size": window}, rot={"base": 1e4, "dims": 64}),
+                                           "right": {"width": width, "blocks": max(1, width // 128), "conv": 4},
+                                           "left_scale": 0.8, "right_scale": 0.5}}
+    delta = {"type": "parallel", "mixer": {"left": dict(att, mask={"size": window}),
+                                           "right": {"heads": heads, "kv_heads": kv_heads, "dim": 128, "vdim": 128, "conv": 4},
+                                           "left_scale": 0.8, "right_scale": 0.5}}
+    out = []
+    for i in range(layers):
+        k = i % 4
+        if k == 0:
+            out.append(dict(blocks, mlp=dense))
+        elif k == 1:
+            out.append(dict(lru, mlp=experts))
+        elif k == 2:
+            out.append({"type": "attention", "mixer": dict(blocks["mixer"], kv_from=i - 2), "mlp": experts})
+        else:
+            out.append(dict(delta, mlp=dense))
+    return {"architecture": "Duvadra", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "residual_mult": 0.5,
+            "logit_softcap": 30.0, "embedding": {"scale": 0.5, "bigram": {"buckets": 65521, "mul_prev": 127, "mul_cur": 17}},
+            "layers": out}
+
+
+def compare_duvadra(size: str, tokens: int, batch: int, steps: int, warmup: int, hbm_gbs: float, bf16_tflops: float):
+    """The Duvadra design beside the Nozizen decoder (the nearest the engine has: a windowed attention, state mixers on
+    the scan kernel, capped or plain gated units beside experts) at equal width, feed-forward, layer count and heads:
+    throughput of both, and how far the kernels of each mechanism are from their rooflines beside the like kernels of the
+    other model.  Rooflines: the scan and the channel recurrence over decoded tokens against the copy bandwidth (every
+    state read and written once); the scan over a prompt against the tensor peak (6 T heads dim vdim operations for the
+    delta rule, 4 for Nozizen's, although the scans run in float32 on the CUDA cores); the channel recurrence over a
+    prompt against the copy bandwidth (inputs, two gate rows in float32 and the gate branch read, the output written);
+    attention over decoded tokens against the copy bandwidth (the keys and values a query sees read once); attention over
+    a prompt against the tensor peak (the causal half, or the window's band), the block attention (mma.sync kernel) and
+    the windowed ones (tcgen05 kernel) apart; the kernels that add to the residual stream and norm it against the copy
+    bandwidth; the experts' products of a prompt against the tensor peak and of decoded tokens against the copy bandwidth
+    (each reached expert read once)."""
+    from .config.duvadra_config import DuvadraConfig
+    from .config.nozizen_config import NozizenConfig
+    sz = DESIGN_SIZES[size]
+    W, ff, H, G, L, V = sz["width"], sz["ff"], sz["heads"], sz["kv_heads"], sz["layers"], sz["vocab"]
+    raw = duvadra_raw_config(W, ff, H, G, L, V)
+    new = measure_design(DuvadraConfig(raw), tokens, batch, steps, warmup)
+    old_raw = nozizen_raw_config(W, ff, H, G, L, V)
+    old = measure_design(NozizenConfig(old_raw), tokens, batch, steps, warmup)
+    D = 128
+    kinds = [layer["type"] for layer in raw["layers"]]
+    n_blocks, n_lru, n_delta = kinds.count("attention"), kinds.count("parallel_2"), kinds.count("parallel")
+    n_moe = sum(1 for layer in raw["layers"] if layer["mlp"]["kind"] == "moe")
+    window = 1024
+    seen = min(tokens, window)
+    band = tokens * tokens / 2 if window >= tokens else tokens * window - window * window / 2
+    o_kinds = [layer["type"] for layer in old_raw["layers"]]
+    o_state, o_att = o_kinds.count("wkv") + o_kinds.count("mamba2"), o_kinds.count("attention")
+    o_moe = sum(1 for layer in old_raw["layers"] if layer["mlp"]["kind"] == "moe")
+    S = old_raw["streams"]
+    F, top, E = ff // 4, 4, 32
+    distinct = E * (1.0 - (1.0 - 1.0 / E) ** (batch * top))
+    frac = lambda work, ms, peak: round(work / (ms * 1e-3) / peak, 4) if ms > 0 else None
+    k_new, k_old, d_new, d_old = new["prefill_kernels"], old["prefill_kernels"], new["decode_kernels"], old["decode_kernels"]
+    att_dec = ("attn_decode", "attn_combine")
+    moe_pf, moe_dec = ("moe_grouped_gemm", "moe_tc5"), ("moe_pair_linear", "moe_grouped_gemm")
+    small = ("attn_prep", "attn_gate", "gated_conv", "conv_state_update", "delta_prep", "head_norm_gate", "scaled_sum",
+             "clamped_glu", "moe_combine", "moe_route", "moe_sort", "moe_gather", "embedding_pair", "last_token")
+    hbm, peak = hbm_gbs * 1e9, bf16_tflops * 1e12
+    row = lambda times, names, work, roof, key: {"ms": round(_kernel_ms(times, *names), 4), key: frac(work, _kernel_ms(times, *names), roof)}
+    kernels = {
+        "decode_scan_duvadra": row(d_new, ("linear_scan",), 2.0 * 4 * D * D * H * n_delta * batch, hbm, "of_hbm"),
+        "decode_scan_nozizen": row(d_old, ("linear_scan",), 2.0 * 4 * D * D * H * o_state * batch, hbm, "of_hbm"),
+        "prefill_scan_duvadra": row(k_new, ("linear_scan",), 6.0 * tokens * D * D * H * n_delta, peak, "of_bf16_peak"),
+        "prefill_scan_nozizen": row(k_old, ("linear_scan",), 4.0 * tokens * D * D * H * o_state, peak, "of_bf16_peak"),
+        "decode_recurrence_duvadra": row(d_new, ("gated_recurrence",), n_lru * batch * W * (2.0 * 4 + 2 + 8 + 2 + 2), hbm, "of_hbm"),
+        "prefill_recurrence_duvadra": row(k_new, ("gated_recurrence", "gated_pieces_combine"), n_lru * tokens * W * (2.0 + 8 + 2 + 2), hbm, "of_hbm"),
+        "decode_attention_duvadra": row(d_new, att_dec, 2.0 * 2 * G * D * batch * (tokens * n_blocks + seen * (n_lru + n_delta)), hbm, "of_hbm"),
+        "decode_attention_nozizen": row(d_old, att_dec, 2.0 * 2 * G * D * seen * batch * o_att, hbm, "of_hbm"),
+        "prefill_attention_blocks_duvadra": row(k_new, ("attn_prefill_kernel",), 4.0 * tokens * tokens / 2 * H * D * n_blocks, peak, "of_bf16_peak"),
+        "prefill_attention_window_duvadra": row(k_new, ("attn_prefill_tc5", "attention_tc5", "merge_key_splits", "tc5_merge"), 4.0 * band * H * D * (n_lru + n_delta), peak, "of_bf16_peak"),
+        "prefill_attention_nozizen": row(k_old, ("attn_prefill", "attention_tc5", "merge_key_splits", "tc5_merge"), 4.0 * band * H * D * o_att, peak, "of_bf16_peak"),
+        # every sublayer: the float32 stream read and written, the sublayer's output read (float32 from the mixers,
+        # bfloat16 from the feed-forwards), the normed rows written
+        "prefill_add_norm_duvadra": row(k_new, ("add_dual_norm",), L * tokens * W * (2.0 * 2 * 4 + 4 + 2 + 2 * 2), hbm, "of_hbm"),
+        "prefill_streams_nozizen": row(k_old, ("hyper_read_norm", "hyper_write"), 2 * L * tokens * W * (2.0 * S * 4 + 2 * 2), hbm, "of_hbm"),
+        "prefill_experts_duvadra": row(k_new, moe_pf, n_moe * 2.0 * tokens * top * 3 * F * W, peak, "of_bf16_peak"),
+        "prefill_experts_nozizen": row(k_old, moe_pf, o_moe * 2.0 * tokens * top * 3 * F * W, peak, "of_bf16_peak"),
+        "decode_experts_duvadra": row(d_new, moe_dec, n_moe * 2.0 * distinct * 3 * F * W, hbm, "of_hbm"),
+        "decode_experts_nozizen": row(d_old, moe_dec, o_moe * 2.0 * distinct * 3 * F * W, hbm, "of_hbm"),
+        "prefill_small_kernels_duvadra": {"ms": round(_kernel_ms(k_new, *small), 4),
+                                          "note": "row preparation and gates of the attentions, convolutions, the delta rule's "
+                                                  "preparation, norms behind the scans, the experts' helpers, the embedding"},
+        "decode_small_kernels_duvadra": {"ms": round(_kernel_ms(d_new, *small), 4)},
+        "decode_add_norm_duvadra": {"ms": round(_kernel_ms(d_new, "add_dual_norm"), 4)},
+    }
+    for r in (new, old):
+        del r["prefill_kernels"], r["decode_kernels"]
+    return {"size": size, "width": W, "ff": ff, "heads": H, "kv_heads": G, "layers": L, "tokens": tokens, "batch": batch,
+            "window": window, "block": 8192, "duvadra": new, "nozizen": old, "kernels": kernels}

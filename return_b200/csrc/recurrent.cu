@@ -1062,7 +1062,7 @@ gated_recurrence_kernel(const TA* __restrict__ u, const float* __restrict__ gate
                         const void* __restrict__ i_bias, const void* __restrict__ lam, int w_dtype, float c_decay,
                         const TA* __restrict__ y, int y_ld, const void* __restrict__ y_bias, float* __restrict__ state,
                         long long state_stride, int s_off, const int* __restrict__ cu_q, const int* __restrict__ seg_slot,
-                        TA* __restrict__ out, int W, int T) {
+                        TA* __restrict__ out, int W, int T, float* __restrict__ log_decay) {
     pdl_wait();
     const int seg = blockIdx.y;
     const int c = blockIdx.x * blockDim.x + threadIdx.x;
@@ -1076,6 +1076,7 @@ gated_recurrence_kernel(const TA* __restrict__ u, const float* __restrict__ gate
     const float rb = load_as_f32(r_bias, w_dtype, c), ib = load_as_f32(i_bias, w_dtype, c);
     const float sp_lam = softplus_f(load_as_f32(lam, w_dtype, c));
     const float yb = y_bias ? load_as_f32(y_bias, w_dtype, c) : 0.f;
+    float lf_sum = 0.f;
     for (int tc = t0; tc < t1; tc += GLR_UNROLL) {
         float ru[GLR_UNROLL], rr[GLR_UNROLL], ri[GLR_UNROLL], ry[GLR_UNROLL];
 #pragma unroll
@@ -1092,25 +1093,56 @@ gated_recurrence_kernel(const TA* __restrict__ u, const float* __restrict__ gate
                 const float r = sigmoid_f(rr[k] + rb), ig = sigmoid_f(ri[k] + ib);
                 const float lf = -c_decay * r * sp_lam;
                 const float f = expf(lf);
+                lf_sum += lf;
                 s = fmaf(f, s, sqrtf(-expm1f(2.f * lf)) * ig * ru[k]);
                 out[(size_t)(tc + k) * W + c] = from_f32<TA>(s * rb_activate(ACT_GELU_TANH, ry[k] + yb, nullptr, 0, 0));
             }
         }
     }
     *sp = s;
+    if (log_decay) log_decay[(size_t)seg * W + c] = lf_sum;     // the segment's transition is exp of this
+}
+
+// A long segment cut into pieces that were walked side by side from zero: per segment and channel, in order,
+// pieces[p] <- carry; carry <- exp(log_decay[p]) * carry + pieces[p], starting from the request's state and leaving the
+// last carry there.  A second walk of the pieces from those states gives the outputs.
+__global__ void __launch_bounds__(128)
+gated_pieces_combine_kernel(float* __restrict__ pieces, const float* __restrict__ log_decay, float* __restrict__ state,
+                            long long state_stride, int s_off, const int* __restrict__ seg_first,
+                            const int* __restrict__ seg_slot, int W) {
+    pdl_wait();
+    const int seg = blockIdx.y;
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= W) return;
+    float* sp = state + (long long)seg_slot[seg] * state_stride + s_off + c;
+    float carry = *sp;
+    for (int p = seg_first[seg]; p < seg_first[seg + 1]; ++p) {
+        const size_t e = (size_t)p * W + c;
+        const float own = pieces[e];
+        pieces[e] = carry;
+        carry = fmaf(expf(log_decay[e]), carry, own);
+    }
+    *sp = carry;
+}
+
+RB_EXPORT int rb_gated_pieces_combine(float* pieces, const float* log_decay, float* state, long long state_stride, int s_off,
+                                      const int* seg_first, const int* seg_slot, int W, int segments, cudaStream_t st) {
+    if (segments <= 0) return 0;
+    return rb_launch_pdl(gated_pieces_combine_kernel, dim3((W + 127) / 128, segments), dim3(128), 0, st, pieces, log_decay, state,
+                         state_stride, s_off, seg_first, seg_slot, W);
 }
 
 RB_EXPORT int rb_gated_recurrence(const void* u, const float* gates, int bs, const void* r_bias, const void* i_bias,
                                   const void* lam, int w_dtype, float c_decay, const void* y, int y_ld, const void* y_bias,
                                   float* state, long long state_stride, int s_off, const int* cu_q, const int* seg_slot,
-                                  void* out, int act_dtype, int W, int T, int segments, cudaStream_t st) {
+                                  void* out, int act_dtype, int W, int T, int segments, float* log_decay, cudaStream_t st) {
     if (segments <= 0) return 0;
     if (bs <= 0 || W % bs) return (int)cudaErrorInvalidValue;
     dim3 grid((W + 127) / 128, segments);
     if (act_dtype == RB_F32)
         return rb_launch_pdl(gated_recurrence_kernel<float>, grid, dim3(128), 0, st, (const float*)u, gates, bs, r_bias, i_bias, lam,
                              w_dtype, c_decay, (const float*)y, y_ld, y_bias, state, state_stride, s_off, cu_q, seg_slot,
-                             (float*)out, W, T);
+                             (float*)out, W, T, log_decay);
     return rb_launch_pdl(gated_recurrence_kernel<bf16>, grid, dim3(128), 0, st, (const bf16*)u, gates, bs, r_bias, i_bias, lam,
-                         w_dtype, c_decay, (const bf16*)y, y_ld, y_bias, state, state_stride, s_off, cu_q, seg_slot, (bf16*)out, W, T);
+                         w_dtype, c_decay, (const bf16*)y, y_ld, y_bias, state, state_stride, s_off, cu_q, seg_slot, (bf16*)out, W, T, log_decay);
 }

@@ -984,8 +984,9 @@ def recurrent_lib() -> ctypes.CDLL:
         lib.rb_rotary_inplace.restype = c_int
         lib.rb_delta_prep.argtypes = [P, I, P, I, I, P, L, I, P, P, P, P, P, P, P, P, P, I, P, I, I, I, I, I, I, F, I, P]
         lib.rb_gated_conv.argtypes = [P, I, P, P, P, I, I, P, L, I, P, P, P, P, P, I, I, I, P]
-        lib.rb_gated_recurrence.argtypes = [P, P, I, P, P, P, I, F, P, I, P, P, L, I, P, P, P, I, I, I, I, P]
-        lib.rb_gated_conv.restype = lib.rb_gated_recurrence.restype = c_int
+        lib.rb_gated_recurrence.argtypes = [P, P, I, P, P, P, I, F, P, I, P, P, L, I, P, P, P, I, I, I, I, P, P]
+        lib.rb_gated_pieces_combine.argtypes = [P, P, P, L, I, P, P, I, I, P]
+        lib.rb_gated_conv.restype = lib.rb_gated_recurrence.restype = lib.rb_gated_pieces_combine.restype = c_int
         lib.rb_conv_state_update.argtypes = [P, I, I, P, L, I, P, P, I, I, I, P]
         lib.rb_head_norm_gate.argtypes = [P, P, I, P, I, I, I, F, P, I, I, I, I, P]
         lib.rb_add_dual_norm.argtypes = [P, P, I, F, P, I, F, P, P, P, I, F, F, P, P, I, I, I, P]
@@ -1136,12 +1137,16 @@ def gated_conv(x, x_bias, taps, conv_bias, state, conv_off: int, batch, out) -> 
            "gated_conv")
 
 
-def gated_recurrence(u, gates, block: int, r_bias, i_bias, lam, c_decay: float, y, y_bias, state, s_off: int, batch, out) -> None:
+def gated_recurrence(u, gates, block: int, r_bias, i_bias, lam, c_decay: float, y, y_bias, state, s_off: int, batch, out,
+                     log_decay=None) -> None:
     """Per channel c and segment, token by token: r = sigmoid(gates[0, b, t, o] + r_bias[c]), i = sigmoid(gates[1, b, t, o]
     + i_bias[c]) with b = c // block, o = c % block (gates float32 [2, W / block, T, block]); log f = -c_decay r
     softplus(lam[c]); s <- f s + sqrt(1 - f^2) i u[t, c]; out[t, c] = s * gelu_tanh(y[t, c] + y_bias[c]).  s is the float32
-    ``state`` row of the request's slot from ``s_off``."""
+    ``state`` row of the request's slot from ``s_off``.  ``log_decay`` (float32 [segments, W]): receives the sum of a
+    segment's log f per channel."""
     T, W = u.shape
+    assert log_decay is None or (log_decay.dtype == torch.float32 and log_decay.is_contiguous()
+                                 and tuple(log_decay.shape) == (batch.num_segments, W))
     assert u.is_contiguous() and out.is_contiguous() and out.shape == (T, W) and out.dtype == u.dtype == y.dtype
     assert gates.dtype == torch.float32 and gates.is_contiguous() and gates.numel() == T * 2 * W and y.stride(1) == 1
     assert r_bias.dtype == i_bias.dtype == lam.dtype and r_bias.numel() == i_bias.numel() == lam.numel() == W
@@ -1149,7 +1154,19 @@ def gated_recurrence(u, gates, block: int, r_bias, i_bias, lam, c_decay: float, 
     _check(recurrent_lib().rb_gated_recurrence(_ptr(u), _ptr(gates), block, _ptr(r_bias), _ptr(i_bias), _ptr(lam),
                                                dtype_code(lam.dtype), c_decay, _ptr(y), y.stride(0), _ptr(y_bias), _ptr(state),
                                                state.stride(0), s_off, _ptr(batch.cu_q), _ptr(batch.seg_slot), _ptr(out),
-                                               dtype_code(u.dtype), W, T, batch.num_segments, _stream()), "gated_recurrence")
+                                               dtype_code(u.dtype), W, T, batch.num_segments, _ptr(log_decay), _stream()),
+           "gated_recurrence")
+
+
+def gated_pieces_combine(pieces, log_decay, state, s_off: int, seg_first, seg_slot, segments: int) -> None:
+    """For a channel recurrence whose long segments were walked in pieces from zero: per segment, in order,
+    ``pieces[p] <- carry; carry <- exp(log_decay[p]) * carry + pieces[p]``, starting from the request's state (``state`` row
+    of its slot from ``s_off``) and leaving the last carry there.  pieces, log_decay: float32 [n_pieces, W]."""
+    assert pieces.dtype == log_decay.dtype == state.dtype == torch.float32 and pieces.is_contiguous() and log_decay.is_contiguous()
+    assert pieces.shape == log_decay.shape and seg_first.dtype == seg_slot.dtype == torch.int32
+    _check(recurrent_lib().rb_gated_pieces_combine(_ptr(pieces), _ptr(log_decay), _ptr(state), state.stride(0), s_off,
+                                                   _ptr(seg_first), _ptr(seg_slot), pieces.shape[1], segments, _stream()),
+           "gated_pieces_combine")
 
 
 def conv_state_update(x, taps_count: int, state, conv_off: int, batch, channels: int) -> None:

@@ -496,6 +496,37 @@ class GatedLinearRecurrence(Mixer):
     def out_projection(self):
         return self.p_o
 
+    # A segment of at least PIECES_MIN_TOKENS tokens is cut into pieces of about PIECE_TOKENS that are walked side by
+    # side (bfloat16 path only: the sums then take another order than token by token, which the float32 path never does).
+    PIECES_MIN_TOKENS = 256
+    PIECE_TOKENS = 64
+
+    def _pieces(self, batch):
+        """None, or (a batch whose segments are the pieces, first piece of every segment, number of pieces) when the step
+        holds a long segment.  Worked out once per step from the host tables."""
+        host = getattr(batch, "host", None)
+        if host is None or not getattr(host, "num_multi", 0):
+            return None
+        memo = getattr(batch, "scratch", None)
+        key = "gated_linear_recurrence.pieces.plan"
+        if memo is not None and key in memo:
+            return memo[key]
+        plan = None
+        lens = np.diff(host.cu_q).astype(np.int64)
+        if int(lens.max()) >= self.PIECES_MIN_TOKENS:
+            cuts, first = [0], [0]
+            for start, n in zip(host.cu_q[:-1], lens):
+                k = int(max(1, n // self.PIECE_TOKENS)) if n >= self.PIECES_MIN_TOKENS else 1
+                cuts.extend(int(start) + (int(n) * i) // k for i in range(1, k + 1))
+                first.append(first[-1] + k)
+            n_pieces = len(cuts) - 1
+            tables = torch.from_numpy(np.asarray(cuts + first + list(range(n_pieces)), np.int32)).to(self.env.device, non_blocking=True)
+            a, c = len(cuts), len(cuts) + len(first)
+            plan = (SimpleNamespace(cu_q=tables[:a], seg_slot=tables[c:], num_segments=n_pieces), tables[a:c], n_pieces)
+        if memo is not None:
+            memo[key] = plan
+        return plan
+
     def forward(self, x, ctx):
         s, b = self.spec, ctx.batch
         T, dev, dt = x.shape[0], x.device, x.dtype
@@ -510,8 +541,20 @@ class GatedLinearRecurrence(Mixer):
         ops.linear_heads(ub, self.p_gate_r, gates[0])
         ops.linear_heads(ub, self.p_gate_i, gates[1])
         mixed = ctx.buffer("gated_linear_recurrence.mixed", (T, W), dt, dev)
-        ops.gated_recurrence(u, gates, bs, self.p_gate_r_bias, self.p_gate_i_bias, self.p_lam, float(s.decay_scale),
-                             proj, self.p_in_bias[:W], ctx.state, 0, b, mixed)
+        args = (u, gates, bs, self.p_gate_r_bias, self.p_gate_i_bias, self.p_lam, float(s.decay_scale), proj, self.p_in_bias[:W])
+        pieces = self._pieces(b) if dt != torch.float32 else None
+        if pieces is None:
+            ops.gated_recurrence(*args, ctx.state, 0, b, mixed)
+        else:
+            # every piece from zero, the states handed on in order (a piece's transition is the product of its tokens'
+            # factors), every piece again from the state it starts with
+            virtual, seg_first, n_pieces = pieces
+            held = ctx.buffer("gated_linear_recurrence.pieces", (n_pieces, W), torch.float32, dev)
+            sums = ctx.buffer("gated_linear_recurrence.piece_decays", (n_pieces, W), torch.float32, dev)
+            held.zero_()
+            ops.gated_recurrence(*args, held, 0, virtual, mixed, log_decay=sums)
+            ops.gated_pieces_combine(held, sums, ctx.state, 0, seg_first, b.seg_slot, b.num_segments)
+            ops.gated_recurrence(*args, held, 0, virtual, mixed)
         y = ctx.buffer("gated_linear_recurrence.y", (T, s.hidden_size), torch.float32, dev)
         ops.linear(mixed, self.p_o, y)
         return y

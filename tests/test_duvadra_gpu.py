@@ -536,6 +536,35 @@ def test_a_prompt_of_many_rows(tmp_path_factory):
         assert_close(got["r1"], want1, dtype, "short")
 
 
+def test_a_long_portion_of_the_channel_recurrence_walked_in_pieces(tmp_path_factory, monkeypatch):
+    """On the bfloat16 path the gated linear recurrence cuts a portion of 256 tokens or more into pieces that are walked
+    at the same time, hands the states from piece to piece and walks again.  The outputs of every piece, the state that
+    the tokens decoded afterwards start from, and a short request in the same step must all be right; the decays are
+    slow, so a state handed on wrongly would show to the end.  The float32 path never cuts."""
+    from return_b200.ext import ops
+    entry = model(tmp_path_factory, "slow_states", slow_states_config(), patch=_slow_decays)
+    reqs = requests_for(entry, (700, 40), seed=80)
+    long_ids, short_ids = reqs["r0"], reqs["r1"]
+    steps = [{"step": 0, "entries": [{"id": "r1", "tokens": short_ids[:30], "want": list(range(30))}], "end": []},
+             {"step": 1, "entries": [{"id": "r0", "tokens": long_ids[:100], "want": list(range(100))},
+                                      {"id": "r1", "tokens": short_ids[30:31], "want": [0]}], "end": []},
+             {"step": 2, "entries": [{"id": "r1", "tokens": short_ids[31:32], "want": [0]},
+                                      {"id": "r0", "tokens": long_ids[100:690], "want": list(range(590))}], "end": []}]
+    for k in range(8):
+        steps.append({"step": 3 + k, "entries": [{"id": "r0", "tokens": [long_ids[690 + k]], "want": [0]},
+                                                  {"id": "r1", "tokens": [short_ids[32 + k]], "want": [0]}],
+                      "end": ["r0", "r1"] if k == 7 else []})
+    calls, combine = [], ops.gated_pieces_combine
+    monkeypatch.setattr(ops, "gated_pieces_combine", lambda *a, **k: (calls.append(a[0].shape[0]), combine(*a, **k))[1])
+    got = run_trace(entry[0], "bfloat16", steps)
+    assert calls == [10]                                              # once, in the step that holds the long portion: nine pieces and the short request
+    assert_close(got["r0"][:698], plain_rows(entry, long_ids)[:698], "bfloat16", "long")
+    assert_close(got["r1"], plain_rows(entry, short_ids), "bfloat16", "short")
+    exact = run_trace(entry[0], "float32", steps)
+    assert len(calls) == 1
+    assert_close(exact["r0"][:698], plain_rows(entry, long_ids)[:698], "float32", "long")
+
+
 # ------------------------------------------------------------------------------- generation through the engine
 
 def _greedy_plain(entry, prompt, n):
