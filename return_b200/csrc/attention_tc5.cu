@@ -34,6 +34,11 @@
 // 224 KB of shared memory and all 512 TMEM columns a CTA (head size 128).  Same contract as the
 // reference's prefill kernel (rollout/attention.py:45-142) and as attention_mma.cu; keys arrive
 // rotated, tiles are aligned to absolute positions, a sliding window bounds the keys from below.
+//
+// The kernel with MOD = true takes a ScoreMod: keys bounded from below by the start of the query's own block of
+// `chunk` positions (instead of a window), scores capped softly (cap * tanh(s / cap)) and a penalty per head that grows
+// with the distance, slopes[h] * (i - j), taken off before the softmax.  A row's thread does that to its 64 scores
+// of a key tile right after it has read them from tensor memory; everything else is the plain kernel.
 // A step with too few such CTAs to fill the GPU (a short portion of a long prompt) splits the keys of every
 // block over gridDim.z CTAs; each leaves its unnormalised O with its reference maximum and sum in float32,
 // and a second kernel merges them (the same arithmetic as the decode kernel's merge).
@@ -126,6 +131,22 @@ struct Paging {
     __device__ __forceinline__ int row(int j) const { return shift >= 0 ? j & (page_size - 1) : j % page_size; }
 };
 
+// tanh(x) = 1 - 2 / (e^(2x) + 1) with the hardware's 2^x and reciprocal: absolute error of a few 1e-7, which is what a
+// capped score needs (the accurate library routine costs ten times the instructions, 64 times a key tile and row).
+__device__ __forceinline__ float fast_tanh(float x) {
+    float e;
+    asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(e) : "f"(x * 2.8853900817779268f));
+    return 1.0f - __fdividef(2.0f, e + 1.0f);
+}
+
+struct ScoreMod {
+    float scale;               // the natural scale (the plain kernel folds log2(e) into its own)
+    float softcap;             // 0: none
+    const float* slopes;       // [Hq] or null
+    int chunk;                 // 0: none
+};
+
+template <bool MOD>
 __global__ void __launch_bounds__(THREADS, 1)
 attn_prefill_tc5_kernel(const bf16* __restrict__ q, int ld, const bf16* __restrict__ kpool,
                         const bf16* __restrict__ vpool, const int* __restrict__ tiles,
@@ -133,7 +154,7 @@ attn_prefill_tc5_kernel(const bf16* __restrict__ q, int ld, const bf16* __restri
                         const int* __restrict__ block_table, int bt_stride, int page_size,
                         bf16* __restrict__ out, int Hq, int Hkv, float scale_log2, int window,
                         float* __restrict__ part_o, float* __restrict__ part_ml, int total_rows,
-                        int* __restrict__ status, const float* __restrict__ sink) {
+                        int* __restrict__ status, const float* __restrict__ sink, ScoreMod sm) {
     // The swizzled tiles need 1024-byte alignment.  The kernel has no static shared memory, so the
     // dynamic window starts at the CTA's shared base; should it ever not be aligned, the kernel
     // reports it and does nothing.
@@ -156,7 +177,8 @@ attn_prefill_tc5_kernel(const bf16* __restrict__ q, int ld, const bf16* __restri
     const int m_rows = min(NQ * QM, cu_q[seg + 1] - q_begin - row0);
     const int p0 = seg_pos0[seg] + row0;                  // position of the CTA's first query
     const int p_last = p0 + m_rows - 1;
-    const int lo_min = window > 0 ? max(0, p0 - window + 1) : 0;
+    const int chunk = MOD ? sm.chunk : 0;
+    const int lo_min = window > 0 ? max(0, p0 - window + 1) : chunk > 0 ? (p0 / chunk) * chunk : 0;
     int jt_first = lo_min / KN;
     // key tiles of each query tile, counted from the first: B (if it has rows) needs all of the block's, A stops earlier
     int na = min(p_last, p0 + QM - 1) / KN - jt_first + 1;
@@ -200,6 +222,11 @@ attn_prefill_tc5_kernel(const bf16* __restrict__ q, int ld, const bf16* __restri
         const int n_mine = qt == 0 ? n_a : n_b;
         const int p0_t = p0 + qt * QM, p_last_t = min(p_last, p0_t + QM - 1);      // the tile's first and last position
         const bool full_tile = m_rows >= (qt + 1) * QM;
+        const int lo_r = chunk > 0 ? (pos_r / chunk) * chunk : 0;               // the first key of this row's own block
+        const float slope = (MOD && sm.slopes) ? sm.slopes[h] : 0.f;
+        const float scale_eff = MOD ? 1.f : scale_log2;                        // the MOD rows hold finished exponents
+        const float cap_l = MOD ? sm.softcap * LOG2E : 0.f, slope_l = slope * LOG2E;
+        const float k_tanh = (MOD && sm.softcap > 0.f) ? sm.scale / sm.softcap * (2.0f * LOG2E) : 0.f;
         unsigned char* myQ = sQ + qt * Q_BYTES;
         unsigned char* myPs = sP + qt * 2 * P_BYTES;           // this query tile's two P buffers
         {
@@ -222,13 +249,45 @@ attn_prefill_tc5_kernel(const bf16* __restrict__ q, int ld, const bf16* __restri
             const int j_base = (jt_begin + t) * KN;
             ok = mbar_wait(bar(B_S_FULL + qt * 2 + (t & 1)), (t >> 1) & 1) && ok;
             fence_after_sync();
-            const bool all_visible = full_tile && j_base + KN - 1 <= p0_t && (window <= 0 || j_base > p_last_t - window);
+            const bool all_visible = full_tile && j_base + KN - 1 <= p0_t && (window <= 0 || j_base > p_last_t - window) &&
+                                     (chunk <= 0 || j_base >= (p_last_t / max(chunk, 1)) * chunk);
             unsigned a[64];
             tmem_ld32(lane_addr + (qt * 2 + (t & 1)) * KN, reinterpret_cast<unsigned(&)[32]>(a[0]));
             tmem_ld32(lane_addr + (qt * 2 + (t & 1)) * KN + 32, reinterpret_cast<unsigned(&)[32]>(a[32]));
             tmem_ld_wait();
             float mx = -INFINITY;
-            if (all_visible) {
+            if (MOD) {
+                // the finished exponent of key j = j_base + i, in units of log2:
+                //   cap L tanh(s scale / cap) - slope L (pos - j)  =  cap L - 2 cap L / (e^(2 s scale / cap) + 1) + slope L i - slope L (pos - j_base)
+                // with L = log2(e): one product, 2^x, one sum, a reciprocal and two fused products a score
+                const float c0 = cap_l - slope_l * (float)(pos_r - j_base);
+                if (sm.softcap > 0.f) {
+#pragma unroll
+                    for (int i = 0; i < 64; ++i) {
+                        float e;
+                        asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(e) : "f"(__uint_as_float(a[i]) * k_tanh));
+                        float rc;
+                        asm("rcp.approx.ftz.f32 %0, %1;\n" : "=f"(rc) : "f"(e + 1.f));
+                        a[i] = __float_as_uint(fmaf(-2.f * cap_l, rc, fmaf(slope_l, (float)i, c0)));
+                    }
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 64; ++i)
+                        a[i] = __float_as_uint(fmaf(__uint_as_float(a[i]), sm.scale * LOG2E, fmaf(slope_l, (float)i, c0)));
+                }
+                if (all_visible) {
+#pragma unroll
+                    for (int i = 0; i < 64; i += 2) mx = max3(mx, __uint_as_float(a[i]), __uint_as_float(a[i + 1]));
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 64; ++i) {
+                        const int j = j_base + i;
+                        const bool vis = row_valid && j <= pos_r && (window <= 0 || j > pos_r - window) && j >= lo_r;
+                        if (!vis) a[i] = 0xff800000u;
+                        mx = fmaxf(mx, __uint_as_float(a[i]));
+                    }
+                }
+            } else if (all_visible) {
 #pragma unroll
                 for (int i = 0; i < 64; i += 2) mx = max3(mx, __uint_as_float(a[i]), __uint_as_float(a[i + 1]));
             } else {
@@ -240,7 +299,7 @@ attn_prefill_tc5_kernel(const bf16* __restrict__ q, int ld, const bf16* __restri
                     mx = fmaxf(mx, __uint_as_float(a[i]));
                 }
             }
-            mx *= scale_log2;                                // the scale is positive: max(scale * s) = scale * max(s)
+            mx *= scale_eff;                                 // the scale is positive: max(scale * s) = scale * max(s)
             // the reference moves only when the maximum has outrun it by RESCALE_STEP (or was -inf)
             float alpha = 1.f;
             bool moved = false;
@@ -272,7 +331,7 @@ attn_prefill_tc5_kernel(const bf16* __restrict__ q, int ld, const bf16* __restri
             }
             unsigned char* myP = myPs + (t & 1) * P_BYTES;
             // p = 2^(scale * s - m), summed in float32, rounded to bfloat16 into the A operand of P V
-            const unsigned long long scale2 = pack2(scale_log2, scale_log2), shift2 = pack2(-mu, -mu);
+            const unsigned long long scale2 = pack2(scale_eff, scale_eff), shift2 = pack2(-mu, -mu);
             unsigned long long sum2 = pack2(0.f, 0.f);
 #pragma unroll
             for (int i = 0; i < 64; i += 2) {
@@ -544,27 +603,47 @@ RB_EXPORT long long rb_attn_tc5_split_floats(int n_split, int total_rows, int Hq
 // tiles: [n_tiles, 2] = (segment, first row of a block of up to 256 query rows), the blocks with the
 // longest contexts first.  n_split > 1 splits the keys of every block over that many CTAs; ``scratch`` then
 // holds rb_attn_tc5_split_floats(...) floats and total_rows is the number of rows of q.
-RB_EXPORT int rb_attn_prefill_tc5(const void* q, int ld, const void* kpool, const void* vpool, const int* tiles,
-                                  int n_tiles, const int* cu_q, const int* seg_pos0, const int* block_table,
-                                  int bt_stride, int page_size, void* out, int Hq, int Hkv, float scale, int window,
-                                  int n_split, void* scratch, int total_rows, int* status, const float* sink,
-                                  cudaStream_t st) {
+// chunk, softcap, slopes: the score options (0, 0, null: the plain kernel); a window and a chunk exclude each other.
+RB_EXPORT int rb_attn_prefill_tc5_mod(const void* q, int ld, const void* kpool, const void* vpool, const int* tiles,
+                                      int n_tiles, const int* cu_q, const int* seg_pos0, const int* block_table,
+                                      int bt_stride, int page_size, void* out, int Hq, int Hkv, float scale, int window,
+                                      int n_split, void* scratch, int total_rows, int* status, const float* sink,
+                                      int chunk, float softcap, const float* slopes, cudaStream_t st) {
     if (n_tiles <= 0) return 0;
     if (n_tiles > 65535 || n_split < 1 || n_split > 64 || (n_split > 1 && scratch == nullptr)) return (int)cudaErrorInvalidValue;
+    if (window > 0 && chunk > 0) return (int)cudaErrorInvalidValue;
     static PerDevice configured;
     const int rc = configured.once([](int) {
-        return cudaFuncSetAttribute(attn_prefill_tc5_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES);
+        cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc5_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(attn_prefill_tc5_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES);
+        return e;
     });
     if (rc != 0) return rc;
     float* part_o = (float*)scratch;
     float* part_ml = part_o ? part_o + (size_t)n_split * total_rows * Hq * D : nullptr;
     dim3 grid(Hq, n_tiles, n_split);
-    attn_prefill_tc5_kernel<<<grid, THREADS, SMEM_BYTES, st>>>(
-        (const bf16*)q, ld, (const bf16*)kpool, (const bf16*)vpool, tiles, cu_q, seg_pos0, block_table, bt_stride,
-        page_size, (bf16*)out, Hq, Hkv, scale * LOG2E, window, part_o, part_ml, total_rows, status, sink);
+    ScoreMod sm;
+    sm.scale = scale; sm.softcap = softcap; sm.slopes = slopes; sm.chunk = chunk;
+    if (chunk > 0 || softcap > 0.f || slopes != nullptr)
+        attn_prefill_tc5_kernel<true><<<grid, THREADS, SMEM_BYTES, st>>>(
+            (const bf16*)q, ld, (const bf16*)kpool, (const bf16*)vpool, tiles, cu_q, seg_pos0, block_table, bt_stride,
+            page_size, (bf16*)out, Hq, Hkv, scale * LOG2E, window, part_o, part_ml, total_rows, status, sink, sm);
+    else
+        attn_prefill_tc5_kernel<false><<<grid, THREADS, SMEM_BYTES, st>>>(
+            (const bf16*)q, ld, (const bf16*)kpool, (const bf16*)vpool, tiles, cu_q, seg_pos0, block_table, bt_stride,
+            page_size, (bf16*)out, Hq, Hkv, scale * LOG2E, window, part_o, part_ml, total_rows, status, sink, sm);
     if (n_split > 1) {
         dim3 mgrid(Hq, n_tiles, NQ * QM / 8);
         merge_key_splits_kernel<<<mgrid, 256, 0, st>>>(part_o, part_ml, tiles, cu_q, n_split, total_rows, Hq, (bf16*)out, sink);
     }
     return rb_launch_status();
+}
+
+RB_EXPORT int rb_attn_prefill_tc5(const void* q, int ld, const void* kpool, const void* vpool, const int* tiles,
+                                  int n_tiles, const int* cu_q, const int* seg_pos0, const int* block_table,
+                                  int bt_stride, int page_size, void* out, int Hq, int Hkv, float scale, int window,
+                                  int n_split, void* scratch, int total_rows, int* status, const float* sink,
+                                  cudaStream_t st) {
+    return rb_attn_prefill_tc5_mod(q, ld, kpool, vpool, tiles, n_tiles, cu_q, seg_pos0, block_table, bt_stride, page_size, out,
+                                   Hq, Hkv, scale, window, n_split, scratch, total_rows, status, sink, 0, 0.f, nullptr, st);
 }

@@ -676,6 +676,8 @@ def attention_tc5_lib(head_dim: int) -> ctypes.CDLL:
         lib = build.load(f"return_attn_tc5_d{head_dim}", ["attention_tc5.cu"], _attn_tc5_defines(head_dim))
         P, I, F = c_void_p, c_int, c_float
         lib.rb_attn_prefill_tc5.argtypes = [P, I, P, P, P, I, P, P, P, I, I, P, I, I, F, I, I, P, I, P, P, P]
+        lib.rb_attn_prefill_tc5_mod.argtypes = [P, I, P, P, P, I, P, P, P, I, I, P, I, I, F, I, I, P, I, P, P, I, F, P, P]
+        lib.rb_attn_prefill_tc5_mod.restype = c_int
         lib.rb_attn_tc5_split_floats.argtypes = [I, I, I]
         lib.rb_attn_tc5_split_floats.restype = ctypes.c_longlong
         lib.rb_attn_prefill_tc5.restype = c_int
@@ -691,11 +693,13 @@ def _sink_ptr(sink, num_heads):
 
 
 def attention_prefill_tc5(qkv, k_pool, v_pool, tiles, cu_q, seg_pos0, block_table, page_size, out, num_heads,
-                          num_kv_heads, head_dim, scale, window=0, num_splits=1, held=None, sink=None) -> None:
+                          num_kv_heads, head_dim, scale, window=0, num_splits=1, held=None, sink=None,
+                          chunk=0, softcap=0.0, slopes=None) -> None:
     """tcgen05 attention for the listed (segment, first row) blocks of up to TC5_TILE_ROWS query rows
     (the blocks with the longest contexts should come first: they take longest).  ``num_splits`` > 1 splits
     every block's keys over that many CTAs and merges them in a second launch; ``held``: the step's map of
-    work buffers, so that the layers share the buffer of the partial results."""
+    work buffers, so that the layers share the buffer of the partial results.  ``chunk``, ``softcap``, ``slopes``: the
+    score options of ``paged_attention``."""
     assert qkv.dtype == torch.bfloat16 and k_pool.dtype == torch.bfloat16 and out.is_contiguous()
     assert tiles.dtype == torch.int32 and tiles.is_contiguous()
     lib = attention_tc5_lib(head_dim)
@@ -709,11 +713,12 @@ def attention_prefill_tc5(qkv, k_pool, v_pool, tiles, cu_q, seg_pos0, block_tabl
             scratch = torch.empty(lib.rb_attn_tc5_split_floats(num_splits, T, num_heads), dtype=torch.float32, device=qkv.device)
             if held is not None:
                 held[key] = scratch
-    _check(lib.rb_attn_prefill_tc5(_ptr(qkv), qkv.stride(0), _ptr(k_pool), _ptr(v_pool), _ptr(tiles),
-                                   tiles.shape[0], _ptr(cu_q), _ptr(seg_pos0), _ptr(block_table),
-                                   block_table.stride(0), page_size, _ptr(out), num_heads, num_kv_heads, scale,
-                                   int(window or 0), num_splits, _ptr(scratch), T, _ptr(tc5_status(qkv.device)),
-                                   _sink_ptr(sink, num_heads), _stream()), "attention_prefill_tc5", 2 if num_splits > 1 else 1)
+    _check(lib.rb_attn_prefill_tc5_mod(_ptr(qkv), qkv.stride(0), _ptr(k_pool), _ptr(v_pool), _ptr(tiles),
+                                       tiles.shape[0], _ptr(cu_q), _ptr(seg_pos0), _ptr(block_table),
+                                       block_table.stride(0), page_size, _ptr(out), num_heads, num_kv_heads, scale,
+                                       int(window or 0), num_splits, _ptr(scratch), T, _ptr(tc5_status(qkv.device)),
+                                       _sink_ptr(sink, num_heads), int(chunk or 0), float(softcap or 0.0),
+                                       _sink_ptr(slopes, num_heads), _stream()), "attention_prefill_tc5", 2 if num_splits > 1 else 1)
 
 
 PREFILL_SPLIT_MIN_KEYS = 512       # a CTA of a split block keeps at least this many keys
@@ -888,9 +893,7 @@ def paged_attention(qkv, k_pool, v_pool, batch, block_table, page_size, out, num
     Options of the score: ``window`` (the last n keys) or ``chunk`` (the keys of the query's own block of n positions,
     blocks counted from position 0), never both; ``sink`` (float32 [heads]: exp(sink) joins the softmax's denominator);
     ``softcap`` (a scaled score s becomes cap * tanh(s / cap)); ``slopes`` (float32 [heads]: slopes[h] * (i - j) is taken
-    off the score of key j for query i).  Scores with a soft cap, slopes or a chunk run on the mma.sync kernels for every
-    head size (the tcgen05 prompt kernel has no such variant)."""
-    modded = bool(chunk) or bool(softcap) or slopes is not None
+    off the score of key j for query i)."""
     if window and chunk:
         raise KernelError("a window and a chunk exclude each other")
     if qkv.dtype == torch.float32:
@@ -905,10 +908,11 @@ def paged_attention(qkv, k_pool, v_pool, batch, block_table, page_size, out, num
     host = batch.host
     bound = window or chunk                       # either bounds the keys a query can see
     if host.num_multi:
-        if head_dim in TC5_ATTENTION_HEAD_DIMS and not modded:
+        if head_dim in TC5_ATTENTION_HEAD_DIMS:
             attention_prefill_tc5(qkv, k_pool, v_pool, batch.tiles[TILES_TC5], batch.cu_q, batch.seg_pos0, block_table,
                                   page_size, out, num_heads, num_kv_heads, head_dim, scale, window or 0,
-                                  _prefill_split_count(batch, num_heads, window), getattr(batch, "scratch", None), sink)
+                                  _prefill_split_count(batch, num_heads, bound), getattr(batch, "scratch", None), sink,
+                                  chunk, softcap, slopes)
         else:
             attention_prefill_mma(qkv, k_pool, v_pool, batch.tiles[TILES_MMA], batch.cu_q, batch.seg_pos0, block_table,
                                   page_size, out, num_heads, num_kv_heads, head_dim, scale, window or 0, sink,

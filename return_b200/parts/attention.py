@@ -160,7 +160,6 @@ class GatedAttention(Mixer):
         self.nk = s.num_kv_heads * s.key_dim if s.own_cache else 0
         self.nv = s.num_kv_heads * s.value_dim if (s.own_cache and not s.values_are_keys) else 0
         self.ng = 0 if s.gate is None else s.num_heads if s.gate == "head" else s.num_heads * s.value_dim
-        self.modded = s.chunk is not None or s.softcap is not None or s.slope_exponent is not None
         self._slopes = None
         self._sink = None
 
@@ -195,7 +194,7 @@ class GatedAttention(Mixer):
     def batch_tilings(self):
         if self.env.act_dtype != torch.bfloat16:
             return {}
-        if self.D in ops.TC5_ATTENTION_HEAD_DIMS and not self.modded:
+        if self.D in ops.TC5_ATTENTION_HEAD_DIMS:
             return {ops.TILES_TC5: Tiling(ops.TC5_TILE_ROWS, heaviest_first=True)}
         return {ops.TILES_MMA: Tiling(ops.MMA_TILE_ROWS)}
 
