@@ -830,8 +830,8 @@ def compare_duvadra(size: str, tokens: int, batch: int, steps: int, warmup: int,
     delta rule, 4 for Nozizen's, although the scans run in float32 on the CUDA cores); the channel recurrence over a
     prompt against the copy bandwidth (inputs, two gate rows in float32 and the gate branch read, the output written);
     attention over decoded tokens against the copy bandwidth (the keys and values a query sees read once); attention over
-    a prompt against the tensor peak (the causal half, or the window's band), the block attention (mma.sync kernel) and
-    the windowed ones (tcgen05 kernel) apart; the kernels that add to the residual stream and norm it against the copy
+    a prompt against the tensor peak (the causal half, or the window's band), the block attention (the kernels with the
+    score options) and the windowed ones (the plain kernel) apart; the kernels that add to the residual stream and norm it against the copy
     bandwidth; the experts' products of a prompt against the tensor peak and of decoded tokens against the copy bandwidth
     (each reached expert read once)."""
     from .config.duvadra_config import DuvadraConfig
@@ -872,8 +872,8 @@ def compare_duvadra(size: str, tokens: int, batch: int, steps: int, warmup: int,
         "prefill_recurrence_duvadra": row(k_new, ("gated_recurrence", "gated_pieces_combine"), n_lru * tokens * W * (2.0 + 8 + 2 + 2), hbm, "of_hbm"),
         "decode_attention_duvadra": row(d_new, att_dec, 2.0 * 2 * G * D * batch * (tokens * n_blocks + seen * (n_lru + n_delta)), hbm, "of_hbm"),
         "decode_attention_nozizen": row(d_old, att_dec, 2.0 * 2 * G * D * seen * batch * o_att, hbm, "of_hbm"),
-        "prefill_attention_blocks_duvadra": row(k_new, ("attn_prefill_kernel",), 4.0 * tokens * tokens / 2 * H * D * n_blocks, peak, "of_bf16_peak"),
-        "prefill_attention_window_duvadra": row(k_new, ("attn_prefill_tc5", "attention_tc5", "merge_key_splits", "tc5_merge"), 4.0 * band * H * D * (n_lru + n_delta), peak, "of_bf16_peak"),
+        "prefill_attention_blocks_duvadra": row(k_new, ("attn_prefill_kernel", "attn_prefill_tc5_kernel<true>"), 4.0 * tokens * tokens / 2 * H * D * n_blocks, peak, "of_bf16_peak"),
+        "prefill_attention_window_duvadra": row(k_new, ("attn_prefill_tc5_kernel<false>", "merge_key_splits", "tc5_merge"), 4.0 * band * H * D * (n_lru + n_delta), peak, "of_bf16_peak"),
         "prefill_attention_nozizen": row(k_old, ("attn_prefill", "attention_tc5", "merge_key_splits", "tc5_merge"), 4.0 * band * H * D * o_att, peak, "of_bf16_peak"),
         # every sublayer: the float32 stream read and written, the sublayer's output read (float32 from the mixers,
         # bfloat16 from the feed-forwards), the normed rows written

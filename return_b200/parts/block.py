@@ -139,17 +139,21 @@ class PreNormBlock(Block):
         a = ctx.buffer("block.normed", (T, H), self.env.act_dtype, stream.device)
         if not (delta is None and pre is not None and pre["position"] == ctx.position and pre["rows"] is a):
             ops.add_dual_norm(stream, (delta,), n1.p_weight, None, n1.spec.eps, n1.spec.offset, a, None)
-        y = self.mixer.forward(a, ctx)
+        if hasattr(self.mixer, "forward_parts"):             # a sum of two mixers: both join the stream in one add
+            (y, s1), (y2, s2) = self.mixer.forward_parts(a, ctx)
+            ys, scales = (y, y2), (m * s1, m * s2)
+        else:
+            ys, scales = (self.mixer.forward(a, ctx),), (m, 1.0)
         if self.feed_forward is not None:
-            ops.add_dual_norm(stream, (y,), n2.p_weight, None, n2.spec.eps, n2.spec.offset, a, None, scales=(m, 1.0))
-            y = self.feed_forward.forward(a, ctx)
+            ops.add_dual_norm(stream, ys, n2.p_weight, None, n2.spec.eps, n2.spec.offset, a, None, scales=scales)
+            ys, scales = (self.feed_forward.forward(a, ctx),), (m, 1.0)
         nxt = ctx.next_block
         if held is not None and isinstance(nxt, PreNormBlock) and nxt._scaled and nxt.mixer_norm.spec.size == H:
             n = nxt.mixer_norm
-            ops.add_dual_norm(stream, (y,), n.p_weight, None, n.spec.eps, n.spec.offset, a, None, scales=(m, 1.0))
+            ops.add_dual_norm(stream, ys, n.p_weight, None, n.spec.eps, n.spec.offset, a, None, scales=scales)
             held["block.prenormed_rows"] = {"rows": a, "position": ctx.position + 1}
         else:
-            ops.add_dual_norm(stream, (y,), None, None, 0.0, 0.0, None, None, scales=(m, 1.0))
+            ops.add_dual_norm(stream, ys, None, None, 0.0, 0.0, None, None, scales=scales)
         return None
 
     def forward(self, stream, delta, ctx):

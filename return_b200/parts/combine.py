@@ -46,12 +46,18 @@ class MixerSum(Mixer):
             out.update(child.graph_variant(n_tokens, longest_context))
         return out
 
-    def forward(self, x, ctx):
+    def forward_parts(self, x, ctx):
+        """((output, scale), (output, scale)) of the two children: a block whose add takes a factor per addend sums them
+        itself, and the weighted sum costs no kernel and no pass over memory of its own."""
         outs = []
         for name, child in self.children.items():
             sub = ctx.children[name]
             sub.position, sub.next_block = ctx.position, None
             outs.append(child.forward(x, sub))
+        return tuple(zip(outs, (float(s) for s in self.spec.scales)))
+
+    def forward(self, x, ctx):
+        outs = [o for o, _ in self.forward_parts(x, ctx)]
         y = ctx.buffer("mixer_sum.y", tuple(outs[0].shape), torch.float32, x.device)
         ops.scaled_sum(outs[0], float(self.spec.scales[0]), outs[1], float(self.spec.scales[1]), y)
         return y
