@@ -795,16 +795,16 @@ def duvadra_raw_config(width: int, ff: int, heads: int, kv_heads: int, layers: i
     fourth feed-forwards are capped gated units, the others 32 experts of a quarter of the dense size each in 8 groups of
     which 4 are kept, four experts a token, so that a token's experts do the dense feed-forward's work."""
     dense = {"kind": "dense", "ff": ff, "limit": 7.0}
-    experts = {"kind": "moe", "router": {"experts": 32, "top": 4, "scale": 2.5, "groups": {"count": 8, "keep": 4}},
+    experts = {"kind": "moe", "router": {"experts": 32, "top": 4, "scale": 2.0, "groups": {"count": 8, "keep": 4}},
                "expert": {"ff": ff // 4}}
     att = {"heads": heads, "kv_heads": kv_heads, "dim": 128, "vdim": 128, "scale": 128 ** -0.5}
-    blocks = {"type": "attention", "mixer": dict(att, softcap=50.0, mask={"size": block})}
+    blocks = {"type": "attention", "mixer": dict(att, softcap=40.0, mask={"size": block})}
     lru = {"type": "parallel_2", "mixer": {"left": dict(att, mask={"size": window}, rot={"base": 1e4, "dims": 64}),
                                            "right": {"width": width, "blocks": max(1, width // 128), "conv": 4},
-                                           "left_scale": 0.8, "right_scale": 0.5}}
+                                           "left_scale": 0.6, "right_scale": 0.9}}
     delta = {"type": "parallel", "mixer": {"left": dict(att, mask={"size": window}),
                                            "right": {"heads": heads, "kv_heads": kv_heads, "dim": 128, "vdim": 128, "conv": 4},
-                                           "left_scale": 0.8, "right_scale": 0.5}}
+                                           "left_scale": 0.9, "right_scale": 0.6}}
     out = []
     for i in range(layers):
         k = i % 4
@@ -816,8 +816,8 @@ def duvadra_raw_config(width: int, ff: int, heads: int, kv_heads: int, layers: i
             out.append({"type": "attention", "mixer": dict(blocks["mixer"], kv_from=i - 2), "mlp": experts})
         else:
             out.append(dict(delta, mlp=dense))
-    return {"architecture": "Duvadra", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "residual_mult": 0.5,
-            "logit_softcap": 30.0, "embedding": {"scale": 0.5, "bigram": {"buckets": 65521, "mul_prev": 127, "mul_cur": 17}},
+    return {"architecture": "Duvadra", "vocab": vocab, "width": width, "norm": {"eps": 1e-5}, "residual_mult": 0.7,
+            "logit_softcap": 20.0, "embedding": {"scale": 2.0, "bigram": {"buckets": 65521, "mul_prev": 1009, "mul_cur": 31}},
             "layers": out}
 
 

@@ -210,18 +210,18 @@ def _segments(lens, slots, pos0=None):
                                  num_tokens=cu[-1])
 
 
-@pytest.mark.parametrize("E,top,count,keep", [(12, 2, 2, 1), (6, 6, 1, 1), (35, 4, 5, 2), (8, 3, 8, 3), (40, 1, 4, 4)])
+@pytest.mark.parametrize("E,top,count,keep", [(15, 2, 3, 1), (6, 6, 1, 1), (35, 4, 5, 2), (8, 3, 8, 3), (40, 1, 4, 4)])
 def test_router_choice(E, top, count, keep):
     """Logistic scores, groups ranked by their two best, the weights over their sum times a factor, against the plain
     router on logits far enough apart that no choice is a close call."""
     from return_b200.ext import ops
     g = torch.Generator().manual_seed(E * 7 + top)
     z = torch.randn((50, E), generator=g) * 2.0
-    r = {"experts": E, "top": top, "scale": 2.5, "groups": {"count": count, "keep": keep}}
+    r = {"experts": E, "top": top, "scale": 1.75, "groups": {"count": count, "keep": keep}}
     picked, wts = plain.route(z.double(), r)
     expert_of = torch.empty((50, top), dtype=torch.int32, device="cuda")
     weight = torch.empty((50, top), dtype=torch.float32, device="cuda")
-    ops.moe_route(z.cuda(), expert_of, weight, top, count, keep, 1e-20, score="sigmoid", group_top=2, scale=2.5)
+    ops.moe_route(z.cuda(), expert_of, weight, top, count, keep, 1e-20, score="sigmoid", group_top=2, scale=1.75)
     got = {(t, int(e)): float(x) for t in range(50) for e, x in zip(expert_of[t].cpu(), weight[t].cpu())}
     want = {(t, int(e)): float(x) for t in range(50) for e, x in zip(picked[t], wts[t])}
     assert got.keys() == want.keys()
@@ -240,10 +240,10 @@ def test_embedding_with_token_pairs(dtype):
     b.tokens = torch.tensor([4, 22, 7, 1, 9, 9], dtype=torch.int32, device="cuda")
     last = torch.tensor([13, 6, 99, 5], dtype=torch.int32, device="cuda")
     out = torch.empty((6, H), dtype=torch.float32, device="cuda")
-    ops.embedding_pair(table.cuda(), pairs.cuda(), b, last, out, 1.5, buckets, 127, 17)
+    ops.embedding_pair(table.cuda(), pairs.cuda(), b, last, out, 1.5, buckets, 113, 29)
     ops.last_token_update(b, last)
     prev = [None, 4, 22, 13, 6, 9]
-    rows = [buckets if p is None else (p * 127 + t * 17) % buckets for p, t in zip(prev, b.tokens.tolist())]
+    rows = [buckets if p is None else (p * 113 + t * 29) % buckets for p, t in zip(prev, b.tokens.tolist())]
     want = table.double()[b.tokens.long().cpu()] * 1.5 + pairs.double()[rows]
     assert torch.allclose(out.cpu().double(), want, rtol=1e-6, atol=1e-6)
     assert last.tolist() == [1, 9, 7, 5]
@@ -304,7 +304,7 @@ ALONE = {
     "window_sink_delta": lambda: config([delta_layer(mlp=None)]),
     "window_rot_lru": lambda: config([lru_layer(mlp=None)]),
     "capped_unit": lambda: config([chunk_layer(mlp=dense(48, 0.5))], bigram=None),
-    "experts": lambda: config([chunk_layer(mlp=moe(12, 2, 16, 2, 1, 2.5))], bigram=None),
+    "experts": lambda: config([chunk_layer(mlp=moe(10, 3, 16, 5, 2, 1.7))], bigram=None),
 }
 
 
