@@ -120,6 +120,120 @@ attn_prep_kernel(const PrepArgs a) {
     }
 }
 
+// The bfloat16 form for sizes that are whole 16-byte pieces (dim, vdim, D, rot, the columns' offsets and the row stride
+// multiples of 8 elements, every pointer aligned): a thread takes eight neighbouring elements of a head at a time, so
+// the projections are read and the rows and pages written in 16-byte accesses.  Same arithmetic, element by element.
+struct Vec8 { float v[8]; };
+__device__ __forceinline__ Vec8 ld8(const bf16* p) {
+    const uint4 raw = *reinterpret_cast<const uint4*>(p);
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+    Vec8 o;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) { const float2 f = __bfloat1622float2(h[j]); o.v[2 * j] = f.x; o.v[2 * j + 1] = f.y; }
+    return o;
+}
+__device__ __forceinline__ void st8(bf16* p, const Vec8& x) {
+    uint4 raw;
+    __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&raw);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) h[j] = __floats2bfloat162_rn(x.v[2 * j], x.v[2 * j + 1]);
+    *reinterpret_cast<uint4*>(p) = raw;
+}
+
+__global__ void __launch_bounds__(256)
+attn_prep_vec_kernel(const PrepArgs a) {
+    __shared__ float scratch[33];
+    pdl_wait();
+    const int t = blockIdx.x, tid = threadIdx.x, nth = blockDim.x;
+    const bf16* row = (const bf16*)a.proj + (size_t)t * a.ld;
+    const int p = a.pos[t];
+    const int nq = a.Hq * a.dim, nk = a.Hkv * a.dim;
+    auto with_bias = [&](const bf16* src, const void* bias, int e) {      // eight projected elements from column e of their part
+        Vec8 x = ld8(src + e);
+        if (bias) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) x.v[j] += load_as_f32(bias, a.bias_dtype, e + j);
+        }
+        return x;
+    };
+    float rq = 1.f, rk = 1.f;
+    if (a.q_norm) {
+        float ss = 0.f;
+        for (int e = tid * 8; e < nq; e += nth * 8) {
+            const Vec8 x = with_bias(row + a.q_off, a.q_bias, e);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) ss = fmaf(x.v[j], x.v[j], ss);
+        }
+        ss = block_sum(ss, scratch);
+        rq = 1.0f / sqrtf(ss / (float)nq + a.eps);
+        if (a.write_kv) {
+            ss = 0.f;
+            for (int e = tid * 8; e < nk; e += nth * 8) {
+                const Vec8 x = with_bias(row + a.k_off, a.k_bias, e);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) ss = fmaf(x.v[j], x.v[j], ss);
+            }
+            ss = block_sum(ss, scratch);
+            rk = 1.0f / sqrtf(ss / (float)nk + a.eps);
+        }
+    }
+    const int half = a.rot >> 1;
+    const float* cs = a.cos_t + (size_t)p * half;
+    const float* sn = a.sin_t + (size_t)p * half;
+    auto finish = [&](Vec8& x, const void* w, float r, int e, int i) {    // norm weights, then the rotation of four pairs
+        if (w) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) x.v[j] *= r * load_as_f32(w, a.norm_dtype, e + j);
+        }
+        if (i < a.rot) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float c = cs[(i >> 1) + j], s = sn[(i >> 1) + j];
+                const float u = x.v[2 * j], v = x.v[2 * j + 1];
+                x.v[2 * j] = u * c - v * s;
+                x.v[2 * j + 1] = v * c + u * s;
+            }
+        }
+    };
+    const int chunks = a.D >> 3;
+    Vec8 zero;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) zero.v[j] = 0.f;
+    bf16* qo = (bf16*)a.q_out + (size_t)t * a.Hq * a.D;
+    for (int c = tid; c < a.Hq * chunks; c += nth) {
+        const int h = c / chunks, i = (c - h * chunks) * 8;
+        Vec8 x = zero;
+        if (i < a.dim) {
+            x = with_bias(row + a.q_off, a.q_bias, h * a.dim + i);
+            finish(x, a.q_norm, rq, h * a.dim + i, i);
+        }
+        st8(qo + (size_t)h * a.D + i, x);
+    }
+    if (!a.write_kv) return;
+    const int page = a.block_table[(size_t)a.tok_seg[t] * a.bt_stride + p / a.page_size];
+    if (page < 0) return;
+    const size_t slot = ((size_t)page * a.Hkv * a.page_size + (size_t)(p % a.page_size)) * a.D;
+    const size_t head_stride = (size_t)a.page_size * a.D;
+    bf16* kp = (bf16*)a.kpool + slot;
+    bf16* vp = (bf16*)a.vpool + slot;
+    for (int c = tid; c < a.Hkv * chunks; c += nth) {
+        const int h = c / chunks, i = (c - h * chunks) * 8;
+        Vec8 x = zero, raw = zero;
+        if (i < a.dim) {
+            x = raw = with_bias(row + a.k_off, a.k_bias, h * a.dim + i);
+            finish(x, a.k_norm, rk, h * a.dim + i, i);
+        }
+        st8(kp + h * head_stride + i, x);
+        if (a.v_off < 0) {
+            st8(vp + h * head_stride + i, i < a.vdim ? raw : zero);
+        } else {
+            Vec8 v = zero;
+            if (i < a.vdim) v = with_bias(row + a.v_off, a.v_bias, h * a.vdim + i);
+            st8(vp + h * head_stride + i, v);
+        }
+    }
+}
+
 RB_EXPORT int rb_attn_prep(const void* proj, int ld, int q_off, int k_off, int v_off, const void* q_bias, const void* k_bias,
                            const void* v_bias, int bias_dtype, const void* q_norm, const void* k_norm, int norm_dtype, float eps,
                            const float* cos_t, const float* sin_t, int rot, const int* pos, const int* tok_seg,
@@ -135,6 +249,11 @@ RB_EXPORT int rb_attn_prep(const void* proj, int ld, int q_off, int k_off, int v
     a.pos = pos; a.tok_seg = tok_seg; a.block_table = block_table; a.bt_stride = bt_stride; a.page_size = page_size;
     a.kpool = kpool; a.vpool = vpool; a.q_out = q_out;
     a.Hq = Hq; a.Hkv = Hkv; a.dim = dim; a.vdim = vdim; a.D = D; a.write_kv = write_kv;
+    auto al = [](const void* p) { return ((uintptr_t)p & 15) == 0; };
+    const bool vec = act_dtype == RB_BF16 && dim % 8 == 0 && vdim % 8 == 0 && D % 8 == 0 && rot % 8 == 0 && ld % 8 == 0 &&
+                     q_off % 8 == 0 && k_off % 8 == 0 && (v_off < 0 || v_off % 8 == 0) && al(proj) && al(q_out) &&
+                     al(kpool) && al(vpool);
+    if (vec) return rb_launch_pdl(attn_prep_vec_kernel, dim3(T), dim3(256), 0, st, a);
     if (act_dtype == RB_F32) return rb_launch_pdl(attn_prep_kernel<float>, dim3(T), dim3(256), 0, st, a);
     return rb_launch_pdl(attn_prep_kernel<bf16>, dim3(T), dim3(256), 0, st, a);
 }
@@ -155,10 +274,42 @@ attn_gate_kernel(TA* __restrict__ o, const TA* __restrict__ gate, int gate_ld, i
     pdl_trigger_late();
 }
 
+// The bfloat16 form for whole 16-byte pieces: eight neighbouring values of a head a thread and round.
+__global__ void __launch_bounds__(256)
+attn_gate_vec_kernel(bf16* __restrict__ o, const bf16* __restrict__ gate, int gate_ld, int g_off, int per_head, int H, int vdim,
+                     int D, size_t n8) {
+    pdl_wait();
+    const int chunks = D >> 3;
+    for (size_t c = (size_t)blockIdx.x * blockDim.x + threadIdx.x; c < n8; c += (size_t)gridDim.x * blockDim.x) {
+        const size_t t = c / ((size_t)H * chunks);
+        const int r = (int)(c - t * H * chunks), h = r / chunks, i = (r - h * chunks) * 8;
+        if (i >= vdim) continue;                            // the padding stays zero
+        Vec8 x = ld8(o + c * 8);
+        if (per_head) {
+            const float g = 1.0f / (1.0f + expf(-to_f32(gate[t * gate_ld + g_off + h])));
+#pragma unroll
+            for (int j = 0; j < 8; ++j) x.v[j] *= g;
+        } else {
+            const Vec8 g = ld8(gate + t * gate_ld + g_off + h * vdim + i);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) x.v[j] = x.v[j] / (1.0f + expf(-g.v[j]));
+        }
+        st8(o + c * 8, x);
+    }
+    pdl_trigger_late();
+}
+
 RB_EXPORT int rb_attn_gate(void* o, const void* gate, int gate_ld, int g_off, int per_head, int act_dtype, int T, int H,
                            int vdim, int D, cudaStream_t st) {
     const size_t n = (size_t)T * H * D;
     if (n == 0) return 0;
+    if (act_dtype == RB_BF16 && D % 8 == 0 && vdim % 8 == 0 && ((uintptr_t)o & 15) == 0 &&
+        (per_head || (gate_ld % 8 == 0 && g_off % 8 == 0 && ((uintptr_t)gate & 15) == 0))) {
+        const size_t n8 = n / 8;
+        const int vblocks = (int)((n8 + 255) / 256 < 8192 ? (n8 + 255) / 256 : 8192);
+        return rb_launch_pdl(attn_gate_vec_kernel, dim3(vblocks), dim3(256), 0, st, (bf16*)o, (const bf16*)gate, gate_ld, g_off,
+                             per_head, H, vdim, D, n8);
+    }
     const int blocks = (int)((n + 255) / 256 < 8192 ? (n + 255) / 256 : 8192);
     if (act_dtype == RB_F32)
         return rb_launch_pdl(attn_gate_kernel<float>, dim3(blocks), dim3(256), 0, st, (float*)o, (const float*)gate, gate_ld, g_off,

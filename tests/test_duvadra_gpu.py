@@ -114,9 +114,9 @@ def wide_config():
     """Sizes that pick the tensor-core kernels of prompts in bfloat16: windowed heads of 64 with a sink and of 128 with a
     rotation, block attention with heads of 96 and of 128, experts with enough pairs for the grouped products."""
     return config([delta_layer(left=attn(heads=4, kv_heads=2, dim=64, vdim=48, size=300), heads=2, kv_heads=1, dim=64, vdim=32, mlp=moe(8, 2, 32, 2, 1)),
-                   chunk_layer(heads=4, kv_heads=4, dim=96, vdim=96, size=256, softcap=30.0, mlp=dense(96)),
+                   chunk_layer(heads=8, kv_heads=4, dim=96, vdim=96, size=256, softcap=30.0, mlp=dense(96)),
                    lru_layer(left=attn(heads=2, kv_heads=1, dim=128, vdim=128, size=700), width=128, blocks=4, conv=4, rot=64, mlp=moe(4, 2, 64, 1, 1)),
-                   chunk_layer(heads=2, kv_heads=1, dim=128, vdim=64, size=1000, mlp=None)], width=64, scale=6.0)
+                   chunk_layer(heads=8, kv_heads=1, dim=128, vdim=64, size=1000, mlp=None)], width=64, scale=6.0)
 
 
 _MODELS = {}
