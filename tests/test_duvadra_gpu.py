@@ -366,6 +366,19 @@ def test_other_sizes(tmp_path_factory, dtype):
     compare(entry, dtype, mixed(reqs, max_live=2, portion=11, decode_tail=9, seed=3), reqs, page_size=4, max_reside=2)
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_many_query_heads_on_one_key_head(tmp_path_factory, dtype):
+    """Twenty and forty query heads a key head: the decode kernel packs a key head's query heads into tiles of 16 rows,
+    and every row keeps its own head's slope, sink and gate."""
+    raw = config([chunk_layer(heads=20, kv_heads=1, dim=16, vdim=16, size=23, mlp=None),
+                  delta_layer(left=attn(heads=40, kv_heads=2, dim=8, vdim=12, size=17), heads=6, kv_heads=1, dim=8, vdim=8, mlp=None),
+                  chunk_layer(heads=36, kv_heads=1, dim=16, vdim=16, size=31, kv_from=0, mlp=dense(24))], width=48)
+    entry = model(tmp_path_factory, "many_heads", raw, seed=9)
+    reqs = requests_for(entry, (70, 33), seed=44)
+    compare(entry, dtype, tail_decoded(reqs, tail=45), reqs, page_size=8)
+    compare(entry, dtype, mixed(reqs, max_live=2, portion=9, decode_tail=20, seed=7), reqs, page_size=4, max_reside=2)
+
+
 # ------------------------------------------------------------------------------- edges, far states, slots
 
 def _slow_decays(tensors):
