@@ -175,7 +175,7 @@ def worst(got, want):
     return float(row_errors(got, want).max())
 
 
-def assert_close(got, want, dtype, what="", mean=0.03):
+def assert_close(got, want, dtype, what="", mean=0.03, robust=False):
     """float32: every row within 1e-4 of its size.  bfloat16: rounding moves single rows far more than the rest (a
     router whose best candidates are nearly tied chooses another expert than the float64 walk does; a head's read-out
     near zero is divided by its own size), so the rows are weighed together: their mean within 3 %, at most one row in
@@ -186,14 +186,17 @@ def assert_close(got, want, dtype, what="", mean=0.03):
         assert float(e.max()) < TOL[dtype], (what, dtype, float(e.max()), int(e.argmax()))
         return
     over = int((e > TOL[dtype]).sum())
+    if robust:            # configurations drawn at random: single rows may move by their own size (see below); the middle row may not
+        assert over <= max(2, e.numel() // 10) and float(e.median()) < mean, (what, dtype, over, float(e.max()), float(e.median()))
+        return
     assert over <= max(2, e.numel() // 10) and float(e.max()) < 0.6 and float(e.mean()) < mean, \
         (what, dtype, over, float(e.max()), float(e.mean()), int(e.argmax()))
 
 
-def compare(entry, dtype, steps, requests, **kw):
+def compare(entry, dtype, steps, requests, robust=False, **kw):
     got = run_trace(entry[0], dtype, steps, **kw)
     for rid, ids in requests.items():
-        assert_close(got[rid], plain_rows(entry, ids), dtype, rid)
+        assert_close(got[rid], plain_rows(entry, ids), dtype, rid, robust=robust)
 
 
 # ------------------------------------------------------------------------------- kernels of single mechanisms
@@ -377,6 +380,68 @@ def test_many_query_heads_on_one_key_head(tmp_path_factory, dtype):
     reqs = requests_for(entry, (70, 33), seed=44)
     compare(entry, dtype, tail_decoded(reqs, tail=45), reqs, page_size=8)
     compare(entry, dtype, mixed(reqs, max_live=2, portion=9, decode_tail=20, seed=7), reqs, page_size=4, max_reside=2)
+
+
+def _random_config(rng):
+    """A configuration no fixed case has: two to five layers of random kinds and sizes (head sizes that fill no vector,
+    odd head counts, windows and blocks from one position to beyond the prompts, taps from one to six, any number of
+    experts and groups), later block attentions reading an earlier one's keys."""
+    width = rng.choice([24, 36, 40, 56, 64])
+    layers, owners = [], []                                    # owners: (layer, kv_heads, dim, vdim) of block attentions with keys
+    for i in range(rng.randint(2, 5)):
+        kind = rng.choice(["attention", "parallel", "parallel_2"])
+        kv = rng.choice([1, 2, 3])
+        heads = kv * rng.choice([1, 2, 3, 5])
+        size = rng.choice([None, 1, 3, 7, 16, 29, 64, 200])
+        mlp = rng.choice([None, dense(rng.choice([7, 24, 40]), rng.choice([0.4, 2.0, 30.0])),
+                          moe(*rng.choice([(4, 1, 16, 2, 1), (6, 2, 8, 3, 2), (9, 3, 12, 3, 3), (5, 5, 8, 1, 1), (16, 4, 8, 4, 2)]),
+                              scale=rng.choice([0.7, 1.0, 3.0]))])
+        if kind == "attention":
+            if owners and rng.random() < 0.5:
+                src, kv, dim, vdim = rng.choice(owners)
+                heads = kv * rng.choice([1, 2, 4])
+                layers.append(chunk_layer(heads=heads, kv_heads=kv, dim=dim, vdim=vdim, size=size, kv_from=src,
+                                          softcap=rng.choice([None, 2.0, 25.0]), mlp=mlp))
+            else:
+                dim, vdim = rng.choice([7, 8, 16, 20, 48]), rng.choice([5, 8, 16, 24, 40])
+                owners.append((i, kv, dim, vdim))
+                layers.append(chunk_layer(heads=heads, kv_heads=kv, dim=dim, vdim=vdim, size=size,
+                                          softcap=rng.choice([None, 2.0, 25.0]), mlp=mlp))
+        elif kind == "parallel":
+            rk = rng.choice([1, 2])
+            layers.append(delta_layer(left=attn(heads=heads, kv_heads=kv, dim=rng.choice([6, 8, 16, 24]), vdim=rng.choice([4, 8, 16, 36]), size=size),
+                                      heads=rk * rng.choice([1, 2, 3]), kv_heads=rk, dim=rng.choice([5, 8, 16, 40]),
+                                      vdim=rng.choice([3, 8, 16, 33]), conv=rng.randint(1, 6),
+                                      scales=(rng.choice([0.3, 1.0]), rng.choice([0.5, 1.2])), mlp=mlp))
+        else:
+            dim = rng.choice([6, 8, 16, 32])
+            blocks = rng.choice([1, 2, 3, 6])
+            layers.append(lru_layer(left=attn(heads=heads, kv_heads=kv, dim=dim, vdim=dim, size=size), width=blocks * rng.choice([1, 4, 7, 16]),
+                                    blocks=blocks, conv=rng.randint(1, 6), rot=rng.choice([0, 2, dim // 2 // 2 * 2, dim]),
+                                    base=rng.choice([50.0, 10000.0]), scales=(rng.choice([0.3, 1.0]), rng.choice([0.5, 1.2])), mlp=mlp))
+    return config(layers, vocab=rng.randint(30, 200), width=width, eps=rng.choice([1e-6, 1e-5, 1e-3]),
+                  mult=rng.choice([None, 0.4, 1.0, 1.3]), bigram=rng.choice([None, (31, 5, 3), (97, 1000003, 7919)]),
+                  scale=rng.choice([None, 0.5, 4.0]), cap=rng.choice([None, 5.0, 40.0]))
+
+
+@pytest.mark.parametrize("seed", list(range(12)))
+def test_random_configurations_and_traces(tmp_path_factory, seed):
+    import random
+    rng = random.Random(500 + seed)
+    raw = _random_config(rng)
+    entry = model(tmp_path_factory, f"fuzz{seed}", raw, seed=seed)
+    reqs = requests_for(entry, [rng.randint(1, 80) for _ in range(rng.randint(2, 4))], seed=100 + seed)
+    steps = mixed(reqs, max_live=rng.randint(1, 3), portion=rng.randint(2, 30), decode_tail=rng.randint(0, 20), seed=seed)
+    page = rng.choice([4, 8, 16, 32])
+    for dtype in ("float32", "bfloat16"):
+        try:
+            # Where bfloat16 turns a router's choice among few experts with large weights, or the sign of the one product
+            # q . k that a delta rule's first token is read out with (its read-out is then divided by its own size), a
+            # single row moves by its own size.  Such rows stay as few as everywhere (two, or one in ten) and the middle
+            # row within 3 %; the float32 rows hold each to 1e-4.
+            compare(entry, dtype, steps, reqs, robust=True, page_size=page, max_reside=3)
+        except AssertionError as e:
+            raise AssertionError((raw, page, str(e)[:300]))
 
 
 # ------------------------------------------------------------------------------- edges, far states, slots
