@@ -643,6 +643,21 @@ def test_a_long_portion_of_the_channel_recurrence_walked_in_pieces(tmp_path_fact
     assert_close(exact["r0"][:698], plain_rows(entry, long_ids)[:698], "float32", "long")
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_blocks_that_begin_inside_the_tensor_core_tiles(tmp_path_factory, dtype):
+    """Block attentions with heads of 64 and 128 (in bfloat16 the tcgen05 kernel's rows of 256 queries and tiles of 64
+    keys) under blocks of 37, 100 and 300 positions, so that every tile of rows holds several blocks' beginnings and whole
+    key tiles that a row may not see; one layer reads another's keys under a larger block."""
+    raw = config([chunk_layer(heads=8, kv_heads=2, dim=64, vdim=64, size=37, mlp=None),
+                  chunk_layer(heads=8, kv_heads=1, dim=128, vdim=128, size=100, softcap=None, mlp=None),
+                  chunk_layer(heads=16, kv_heads=2, dim=64, vdim=64, size=300, kv_from=0, softcap=20.0, mlp=dense(64))], width=64)
+    entry = model(tmp_path_factory, "tile_blocks", raw, seed=13)
+    reqs = requests_for(entry, (700, 90), seed=71)
+    compare(entry, dtype, whole(reqs), reqs)
+    compare(entry, dtype, portions(reqs, [300, 2, 257, 64, 70]), reqs, page_size=16)
+    compare(entry, dtype, tail_decoded({"r0": reqs["r0"][:400]}, tail=40), {"r0": reqs["r0"][:400]}, page_size=8)
+
+
 # ------------------------------------------------------------------------------- generation through the engine
 
 def _greedy_plain(entry, prompt, n):
